@@ -10,6 +10,8 @@ a cache) are sorted into groups by what they need:
   blocks back as soon as every position in them has fallen out of the window.
 * every entry with a `StateNeed` has a tensor [slots, *shape]: state of fixed
   size per sequence, zeroed when a slot is taken.
+* an entry with a `MultiNeed` holds one of the above for each of its parts (an attention
+  layer that also keeps a little running state beside its keys and values).
 
 Each sequence has its own length. Storage is sized by `max_tokens`, the most
 positions that live sequences hold at any time with each sequence's count
@@ -27,7 +29,7 @@ import torch
 
 from ..errors import allocate
 from .allocator import CacheFull, Pool
-from .needs import KVNeed, StateNeed
+from .needs import KVNeed, MultiNeed, StateNeed
 
 BLOCK = 64
 
@@ -43,6 +45,7 @@ class EntryView:
     block_table: torch.Tensor | None = None   # int32 [B, max_blocks], this step's sequences
     state: torch.Tensor | None = None         # [slots, *shape]; index with the step's slots
     group: int = -1
+    parts: list | None = None                 # a `MultiNeed`'s views, one for each of its needs
 
 
 class KVGroup:
@@ -89,18 +92,26 @@ class SequenceCache:
         self.groups: list[KVGroup] = []
         self.entry_group: dict[int, tuple[int, int]] = {}     # entry -> (group, index in group)
         self.states: dict[int, torch.Tensor] = {}
-        by_need: dict[KVNeed, list[int]] = {}
-        for entry, need in enumerate(self.needs):
+        by_need: dict[KVNeed, list] = {}
+
+        def place(key, need):
+            # `key`: the entry's number, or (entry, part) for a part of a `MultiNeed`
             if isinstance(need, KVNeed):
-                by_need.setdefault(need, []).append(entry)
+                by_need.setdefault(need, []).append(key)
             elif isinstance(need, StateNeed):
                 shape = (self.max_slots,) + tuple(need.shape)
-                self.states[entry] = allocate(
+                self.states[key] = allocate(
                     lambda: torch.zeros(shape, dtype=_DTYPES[need.dtype], device=device),
-                    f"the per-sequence state of cache entry {entry}",
+                    f"the per-sequence state of cache entry {key}",
                     int(np.prod(shape)) * _DTYPES[need.dtype].itemsize)
+            elif isinstance(need, MultiNeed) and not isinstance(key, tuple):
+                for i, part in enumerate(need.parts):
+                    place((key, i), part)
             elif need is not None:
-                raise TypeError(f"cache entry {entry}: unknown need {need!r}")
+                raise TypeError(f"cache entry {key}: unknown need {need!r}")
+
+        for entry, need in enumerate(self.needs):
+            place(entry, need)
         for need, entries in by_need.items():
             g = len(self.groups)
             self.groups.append(KVGroup(need, entries, self.blocks, self.max_blocks_per_seq,
@@ -211,8 +222,11 @@ class SequenceCache:
         index = np.asarray(list(slots), dtype=np.int64)
         return [group.tables[index] for group in self.groups]
 
-    def entry_view(self, entry: int, device_tables: list) -> EntryView:
-        need = self.needs[entry]
+    def entry_view(self, entry, device_tables: list, need=None) -> EntryView:
+        need = self.needs[entry] if need is None else need
+        if isinstance(need, MultiNeed):
+            return EntryView(need, parts=[self.entry_view((entry, i), device_tables, part)
+                                          for i, part in enumerate(need.parts)])
         if isinstance(need, KVNeed):
             g, i = self.entry_group[entry]
             group = self.groups[g]

@@ -37,3 +37,10 @@ class StateNeed:
     live sequence, zero when the sequence starts."""
     shape: tuple
     dtype: str = "float32"
+
+
+@dataclass(frozen=True)
+class MultiNeed:
+    """Several needs of one layer call (keys and values AND a small running state, say): the
+    call's `EntryView.parts` lists a view for each, in this order."""
+    parts: tuple

@@ -23,19 +23,29 @@ def known_architectures() -> list[str]:
 
 
 def architecture_name(raw: dict) -> str:
+    """The model class a config.json names: the first entry of its `architectures` list, or
+    the string under `architecture`."""
+    if isinstance(raw.get("architecture"), str) and "architectures" not in raw:
+        return raw["architecture"]
     names = raw.get("architectures")
     if not isinstance(names, (list, tuple)) or not names or not isinstance(names[0], str):
-        raise ConfigError("config.json has no `architectures` list naming the model class; "
+        raise ConfigError("config.json has neither an `architectures` list nor an "
+                          "`architecture` string naming the model class; "
                           f"known architectures: {', '.join(known_architectures())}")
     return names[0]
 
 
-def config_from_dict(raw: dict):
+def config_from_dict(raw: dict, tensor_shapes: dict | None = None):
+    """`tensor_shapes` (tensor name -> shape, from a checkpoint's header): for architectures
+    whose config.json leaves a size to the tensors (`needs_tensor_shapes` on the class)."""
     name = architecture_name(raw)
     if name not in _ARCHITECTURES:
         raise ConfigError(f"architecture {name!r} is not registered; known architectures: "
                           f"{', '.join(known_architectures())}")
-    return _ARCHITECTURES[name].from_dict(raw)
+    cls = _ARCHITECTURES[name]
+    if getattr(cls, "needs_tensor_shapes", False):
+        return cls.from_dict(raw, tensor_shapes)
+    return cls.from_dict(raw)
 
 
 def config_from_folder(folder):
@@ -49,4 +59,17 @@ def config_from_folder(folder):
         raise ConfigError(f"{path} is not JSON: {exc}") from None
     if not isinstance(raw, dict):
         raise ConfigError(f"{path} does not hold a JSON object")
-    return config_from_dict(raw)
+    shapes = None
+    try:
+        cls = _ARCHITECTURES.get(architecture_name(raw))
+    except ConfigError:
+        cls = None
+    if getattr(cls, "needs_tensor_shapes", False):
+        from ..weights.loader import Checkpoint
+        from ..weights.safetensors_io import WeightError
+        try:
+            checkpoint = Checkpoint(folder)
+            shapes = {n: tuple(checkpoint.info(n).shape) for n in checkpoint.names()}
+        except WeightError:
+            shapes = None          # the loader will say what is wrong with the folder
+    return config_from_dict(raw, shapes)

@@ -25,9 +25,12 @@ class ConfigError(ValueError):
 
 @dataclass(frozen=True)
 class NormSpec:
+    """`suffix` is what the norm's weight is called after the norm's own name
+    (".weight" in most checkpoints, nothing in some)."""
     size: int
     eps: float
     kind: str = "rms_norm"
+    suffix: str = ".weight"
 
 
 @dataclass(frozen=True)
@@ -70,6 +73,65 @@ class GatedMLPSpec:
 
 
 @dataclass(frozen=True)
+class LogDistanceAttentionSpec:
+    """Grouped-query causal self-attention without a rotation: the score of query i on key
+    j is `q.k * scale - slope[h] * ln(1 + rate[h] * (i - j))`, with two learned numbers a
+    head, so that far keys lose weight smoothly. Values may have a width of their own
+    (`value_dim`), the projections may have biases, and each head's output may be
+    multiplied by a gate `sigmoid(Wg x)[h]`, one number a head, before the output
+    projection. `window` as in `AttentionSpec`.
+
+    Tensor names after the part's prefix: `q`, `k`, `v`, `o` (+ `.b` for biases), `g` for
+    the gate's rows, `r1` (slopes) and `r2` (rates)."""
+    hidden: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    window: Optional[int]
+    qkv_bias: bool = True
+    out_bias: bool = True
+    head_gate: bool = True
+    kind: str = "log_distance_attention"
+
+
+@dataclass(frozen=True)
+class DeltaRuleSpec:
+    """A linear-recurrent mixer whose state, one `head_dim x head_dim` matrix a head, is
+    decayed channel by channel, has the part that lies along the current unit key partly
+    removed, and gets the outer product of key and value added (a delta rule with a
+    removal rate a channel):
+
+        S <- diag(w) S - (a * u)(u^T S) + k v^T,    out = S^T r
+
+    with w = exp(-decay_scale * sigmoid(w0 + W2 tanh(W1 x))) from a low-rank pair of
+    matrices of inner size `decay_rank`, a = sigmoid(Wa x + b), and u = k / sqrt(|k|^2 +
+    `key_eps`). Each head's output is divided by its root mean square (`eps` inside the
+    root), multiplied by a weight and by `sigmoid(Wg x)`, and projected.
+
+    Tensor names after the part's prefix: `r`, `k`, `v`, `g`, `a`, `a.b`, `w1`, `w2`, `w0`,
+    `norm`, `o`."""
+    hidden: int
+    heads: int
+    head_dim: int
+    decay_rank: int
+    eps: float
+    decay_scale: float = 0.6065306597126334      # exp(-1/2)
+    key_eps: float = 1e-6
+    kind: str = "general_delta"
+
+
+@dataclass(frozen=True)
+class DenseMLPSpec:
+    """Dense feed-forward without a gate: `down(act(up(x)))`; tensors `up` and `down`."""
+    hidden: int
+    intermediate: int
+    activation: str = "gelu_tanh"
+    kind: str = "dense_mlp"
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     """One layer: how a mixer and a feed-forward are arranged around the residual.
 
@@ -86,6 +148,35 @@ class BlockSpec:
     mixer_norm_name: str = "input_layernorm"
     ffn_norm_name: str = "post_attention_layernorm"
     kind: str = "pre_norm"
+
+
+@dataclass(frozen=True)
+class StreamBlockSpec:
+    """A pre-norm layer over `streams` copies of the residual stream. Each sublayer reads a
+    weighted sum of the streams and writes back to all of them:
+
+        u = sum_s in[s] x_s;  y = sublayer(norm(u));  x_t <- sum_s mix[s, t] x_s + out[t] y
+
+    (`connections` False: one stream and the plain `x += y`). With `token_shift` the
+    mixer's input h is blended with the previous token's, `h + (h_prev - h) * shift`,
+    element by element; the previous token's h is per-sequence state. `ffn` None: the layer
+    has no feed-forward.
+
+    Tensor names after `prefix`: the norms' (`mixer_norm_name`, `ffn_norm_name`),
+    `hc1.in`, `hc1.out`, `hc1.mix` for the mixer and `hc2.*` for the feed-forward, `shift`."""
+    prefix: str
+    mixer: object
+    mixer_norm: NormSpec
+    ffn: object
+    ffn_norm: Optional[NormSpec]
+    streams: int = 1
+    connections: bool = False
+    token_shift: bool = False
+    mixer_name: str = "mix"
+    ffn_name: str = "mlp"
+    mixer_norm_name: str = "norm1"
+    ffn_norm_name: str = "norm2"
+    kind: str = "stream_block"
 
 
 @dataclass(frozen=True)
@@ -129,6 +220,7 @@ class ModelSpec:
     logit_softcap: Optional[float] = None
     head_bias_name: Optional[str] = None
     ignore_tensors: tuple = ()
+    streams: int = 1
 
     def cache_entries(self) -> int:
         return 1 + max((c.cache for c in self.run_order), default=-1)

@@ -47,6 +47,9 @@ LIBRARIES = {
     "gemm_wide": "gemm_wide.cu",
     "gemm_pair": "gemm_pair.cu",
     "gemm_lib": "gemm_lib.cu",
+    "streams": "streams.cu",
+    "delta_rule": "delta_rule.cu",
+    "attention_distance": "attention_distance.cu",
 }
 
 #: extra flags of single libraries (libraries that need the driver API, for instance)

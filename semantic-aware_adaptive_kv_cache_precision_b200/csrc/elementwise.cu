@@ -1,4 +1,4 @@
-// Embedding gather, gated activation, residual add, row gather.
+// Embedding gather, gated and plain activations, residual add, row gather.
 //
 // The reference's versions: `src/core_kernels/embed.cu:27-43` (an id outside the
 // table gives a zero row), `src/core_kernels/swiglu.cu:26-38`
@@ -106,7 +106,35 @@ __global__ void scale_cap_kernel(float* __restrict__ x, long long count, float s
   }
 }
 
+// The tanh form of GELU, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), in fp32 with one
+// rounding at the store.
+template <typename T>
+__global__ void gelu_tanh_kernel(const T* __restrict__ in, T* __restrict__ out, long long count) {
+  let_next_kernel_start();
+  wait_for_previous_kernel();
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float z = widen(in[i]);
+    const float inner = 0.7978845608028654f * fmaf(0.044715f * z * z, z, z);
+    out[i] = narrow<T>(0.5f * z * (1.f + tanhf(inner)));
+  }
+}
+
 }  // namespace
+
+SAKV_EXPORT int sakv_gelu_tanh(const void* in, void* out, int dtype, long long count,
+                               cudaStream_t stream) {
+  if (count < 0) return cudaErrorInvalidValue;
+  if (count == 0) return 0;
+  const dim3 grid(grid_for(count, 256)), block(256);
+  if (dtype == SAKV_F32)
+    return launch_overlapped(gelu_tanh_kernel<float>, grid, block, 0, stream, 1, (const float*)in,
+                             (float*)out, count);
+  if (dtype == SAKV_BF16)
+    return launch_overlapped(gelu_tanh_kernel<__nv_bfloat16>, grid, block, 0, stream, 1,
+                             (const __nv_bfloat16*)in, (__nv_bfloat16*)out, count);
+  return cudaErrorInvalidValue;
+}
 
 SAKV_EXPORT int sakv_scale_cap(float* x, long long count, float scale, float cap,
                                cudaStream_t stream) {

@@ -96,11 +96,24 @@ class DecoderModel:
         `final_states` gives the entry that closes that list."""
         if self.arena is None:
             raise RuntimeError("no weights on the device; load a checkpoint first")
-        x = ops.embed(step.token_ids, self.embed)
-        if self.spec.embed_scale != 1.0:
-            ops.scale_cap_(x, self.spec.embed_scale)
+        streams = getattr(self.spec, "streams", 1)
+        if streams > 1:          # every stream starts as the embedding's output
+            x = torch.empty((streams, step.tokens, self.spec.hidden), dtype=torch.float32,
+                            device=self.device)
+            ops.embed(step.token_ids, self.embed, out=x[0])
+            if self.spec.embed_scale != 1.0:
+                ops.scale_cap_(x[0], self.spec.embed_scale)
+            ops.streams_spread(x)
+        else:
+            x = ops.embed(step.token_ids, self.embed)
+            if self.spec.embed_scale != 1.0:
+                ops.scale_cap_(x, self.spec.embed_scale)
+
+        def stream(x):           # what the streams stand for: their sum
+            return ops.streams_step(x, reduce=True) if x.dim() == 3 else x.clone()
+
         if capture is not None:
-            capture.append(x.clone())
+            capture.append(stream(x))
         written = set()
         pending = None          # a block's last output, not yet added to the stream
         last = len(self.spec.run_order) - 1
@@ -112,15 +125,15 @@ class DecoderModel:
                                         leave_pending=i < last and capture is None)
             else:
                 if pending is not None:
-                    ops.add_into(x, pending)
+                    _settle(x, pending)
                 block.forward(x, step, view, call.cache not in written)
                 pending = None
             written.add(call.cache)
             if capture is not None and i < last:
-                capture.append(x.clone())
+                capture.append(stream(x))
         if pending is not None:
-            ops.add_into(x, pending)
-        return x
+            _settle(x, pending)
+        return ops.streams_step(x, reduce=True) if x.dim() == 3 else x
 
     def final_states(self, x: torch.Tensor) -> torch.Tensor:
         """The stream after the final norm, fp32 [T, hidden]: the last entry of the captured
@@ -135,6 +148,15 @@ class DecoderModel:
         if self.spec.logit_scale != 1.0 or self.spec.logit_softcap:
             ops.scale_cap_(out, self.spec.logit_scale, self.spec.logit_softcap)
         return out
+
+
+def _settle(x, pending) -> None:
+    """Add what a block left pending: a plain fp32 delta, or an update that knows how it
+    goes into the streams."""
+    if hasattr(pending, "apply"):
+        pending.apply(x)
+    else:
+        ops.add_into(x, pending)
 
 
 def _strip(name: str) -> str:

@@ -14,6 +14,8 @@ from ._lib import (BF16, CACHE_BLOCK, F32, KernelError, call, dtype_code, plain_
                    require_cuda)
 from .linear import Deferred, gated_up, linear
 from . import gemm_tc
+from .streams import streams_spread, streams_step, token_shift
+from .recurrent import delta_rule
 from .attention import (attention_decode, attention_prefill, attention_prefill_tc, decode_splits,
                         forget_descriptors,
                         fast_path_takes, kernel_errors, plan_wide_tiles, tc_prefill_takes, upload_query_tiles,
@@ -23,7 +25,8 @@ __all__ = ["CACHE_BLOCK", "KernelError", "embed", "rms_norm", "rope_store", "att
            "attention_decode", "attention_prefill", "attention_prefill_tc", "tc_prefill_takes", "plan_wide_tiles", "upload_wide_plan",
            "upload_query_tiles",
            "decode_splits", "fast_path_takes", "forget_descriptors",
-           "kernel_errors", "gated_silu", "gated_up", "gemm_tc", "add_into", "scale_cap_", "linear", "choose", "Deferred"]
+           "kernel_errors", "gated_silu", "gelu_tanh", "streams_step", "streams_spread", "token_shift",
+           "delta_rule", "kv_store", "distance_attention", "gated_up", "gemm_tc", "add_into", "scale_cap_", "linear", "choose", "Deferred"]
 
 
 def _check(cond: bool, message: str) -> None:
@@ -136,6 +139,70 @@ def gated_silu(gate_up: torch.Tensor) -> torch.Tensor:
     tokens, inter = gate_up.shape[0], gate_up.shape[1] // 2
     out = torch.empty((tokens, inter), dtype=gate_up.dtype, device=gate_up.device)
     call("sakv_gated_silu", ptr(gate_up), ptr(out), dtype_code(gate_up.dtype), tokens, inter)
+    return out
+
+
+def gelu_tanh(x: torch.Tensor) -> torch.Tensor:
+    """The tanh form of GELU, element by element (fp32 inside, x's type outside)."""
+    require_cuda(x)
+    _check(x.is_contiguous(), "gelu_tanh: contiguous input")
+    out = torch.empty_like(x)
+    call("sakv_gelu_tanh", ptr(x), ptr(out), dtype_code(x.dtype), x.numel())
+    return out
+
+
+def kv_store(qkv: torch.Tensor, k_off: int, v_off: int, positions: torch.Tensor,
+             token_seq: torch.Tensor, block_table: torch.Tensor, k_cache: torch.Tensor,
+             v_cache: torch.Tensor) -> None:
+    """Copy a step's keys (`qkv[:, k_off:]`, kv_heads * dim wide) and values (`qkv[:, v_off:]`,
+    kv_heads * vdim wide) into the cache entry: keys [blocks, kv_heads, 64, dim], values
+    [blocks, kv_heads, 64, vdim]."""
+    require_cuda(qkv, positions, token_seq, block_table, k_cache, v_cache)
+    tokens = qkv.shape[0]
+    _check(qkv.dim() == 2 and qkv.stride(1) == 1, "qkv: [T, columns] with contiguous rows")
+    for c in (k_cache, v_cache):
+        _check(c.dtype == qkv.dtype and c.is_contiguous() and c.dim() == 4
+               and c.shape[2] == CACHE_BLOCK and c.shape[1] == k_cache.shape[1],
+               "cache entry: [blocks, kv_heads, 64, width] of the activations' type")
+    kv_heads, dim, vdim = k_cache.shape[1], k_cache.shape[3], v_cache.shape[3]
+    _check(k_off + kv_heads * dim <= qkv.shape[1] and v_off + kv_heads * vdim <= qkv.shape[1],
+           "keys or values reach beyond qkv's columns")
+    _check(block_table.dtype == torch.int32 and block_table.dim() == 2
+           and block_table.is_contiguous(), "block_table: int32 [B, max_blocks]")
+    call("sakv_kv_store", ptr(qkv), dtype_code(qkv.dtype), qkv.stride(0), k_off, v_off,
+         ptr(positions), ptr(token_seq), ptr(block_table), block_table.shape[1], ptr(k_cache),
+         ptr(v_cache), tokens, kv_heads, dim, vdim)
+
+
+def distance_attention(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                       positions: torch.Tensor, token_seq: torch.Tensor,
+                       block_table: torch.Tensor, heads: int, scale: float, window: int | None,
+                       slope: torch.Tensor | None, rate: torch.Tensor | None,
+                       gate_off: int | None = None) -> torch.Tensor:
+    """Causal grouped-query attention of every token of the step over its sequence's cache
+    with the score `q.k * scale - slope[h] * ln(1 + rate[h] * distance)`; queries are the first
+    heads * dim columns of `qkv`, and with `gate_off` each head's output is multiplied by
+    `sigmoid(qkv[:, gate_off + h])`. Returns [T, heads * vdim] of qkv's type."""
+    require_cuda(qkv, k_cache, v_cache, positions, token_seq, block_table, slope, rate)
+    tokens = qkv.shape[0]
+    kv_heads, dim, vdim = k_cache.shape[1], k_cache.shape[3], v_cache.shape[3]
+    _check(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= heads * dim,
+           "qkv: [T, >= heads * dim]")
+    _check(heads % kv_heads == 0, "heads must be a multiple of kv_heads")
+    for c in (k_cache, v_cache):
+        _check(c.dtype == qkv.dtype and c.is_contiguous() and c.dim() == 4
+               and c.shape[2] == CACHE_BLOCK and c.shape[1] == kv_heads,
+               "cache entry: [blocks, kv_heads, 64, width] of the activations' type")
+    _check((slope is None) == (rate is None), "slope and rate come together")
+    for c in (slope, rate):
+        _check(c is None or (c.dtype == torch.float32 and c.shape == (heads,)
+                             and c.is_contiguous()), "slope, rate: fp32 [heads]")
+    _check(gate_off is None or 0 <= gate_off <= qkv.shape[1] - heads, "gate_off: inside qkv")
+    out = torch.empty((tokens, heads * vdim), dtype=qkv.dtype, device=qkv.device)
+    call("sakv_distance_attention", ptr(qkv), dtype_code(qkv.dtype), qkv.stride(0),
+         -1 if gate_off is None else int(gate_off), ptr(out), ptr(k_cache), ptr(v_cache),
+         ptr(positions), ptr(token_seq), ptr(block_table), block_table.shape[1], tokens, heads,
+         kv_heads, dim, vdim, float(scale), int(window) if window else 0, ptr(slope), ptr(rate))
     return out
 
 

@@ -5,8 +5,12 @@ from .base import Part, build_part, register_part
 from .norm import RMSNorm
 from .rotary import NoPosition, RotaryHalf
 from .attention import GQAAttention
-from .mlp import GatedMLP
+from .mlp import DenseMLP, GatedMLP
 from .block import PreNormBlock
+from .delta_rule import DeltaRuleMixer
+from .distance_attention import LogDistanceAttention
+from .streams import StreamBlock, StreamUpdate
 
 __all__ = ["Part", "build_part", "register_part", "RMSNorm", "RotaryHalf", "NoPosition",
-           "GQAAttention", "GatedMLP", "PreNormBlock"]
+           "GQAAttention", "GatedMLP", "DenseMLP", "PreNormBlock", "DeltaRuleMixer",
+           "LogDistanceAttention", "StreamBlock", "StreamUpdate"]

@@ -42,4 +42,33 @@ class GatedMLP(Part):
         return out.delta if isinstance(out, ops.Deferred) else None
 
 
+class DenseMLP(Part):
+    """Dense feed-forward without a gate, `down(act(up(h)))`, with the tanh form of GELU
+    (fp32 inside, one rounding at its store); tensors `up` and `down`."""
+
+    def __init__(self, spec, prefix, mode):
+        super().__init__(spec, prefix, mode)
+        if spec.activation != "gelu_tanh":
+            raise ValueError(f"activation {spec.activation!r}: only 'gelu_tanh' is built")
+
+    def tensor_decls(self):
+        s, p = self.spec, self.prefix
+        return [TensorDecl(p + "up", (s.intermediate, s.hidden)),
+                TensorDecl(p + "down", (s.hidden, s.intermediate))]
+
+    def bind(self, arena):
+        self.w_up = arena.view(self.prefix + "up")
+        self.w_down = arena.view(self.prefix + "down")
+
+    def produce(self, h, step):
+        """The feed-forward's output, fp32 [T, hidden]."""
+        act = ops.gelu_tanh(ops.linear(h, self.w_up, out_dtype=self.act_dtype))
+        return ops.linear(act, self.w_down, out_dtype=torch.float32)
+
+    def forward(self, h, step, residual):
+        ops.linear(ops.gelu_tanh(ops.linear(h, self.w_up, out_dtype=self.act_dtype)),
+                   self.w_down, accumulate_into=residual)
+
+
 register_part("gated_mlp", GatedMLP)
+register_part("dense_mlp", DenseMLP)

@@ -11,13 +11,17 @@ from .base import Part, register_part
 
 
 class RMSNorm(Part):
-    """`prefix` is the tensor's name without '.weight'."""
+    """`prefix` is the tensor's name without the spec's suffix ('.weight' by default)."""
+
+    @property
+    def weight_name(self):
+        return self.prefix + getattr(self.spec, "suffix", ".weight")
 
     def tensor_decls(self):
-        return [TensorDecl(self.prefix + ".weight", (self.spec.size,), init="ones_normal")]
+        return [TensorDecl(self.weight_name, (self.spec.size,), init="ones_normal")]
 
     def bind(self, arena):
-        self.weight = arena.view(self.prefix + ".weight")
+        self.weight = arena.view(self.weight_name)
 
     folds_add = True     # forward(x, add=delta) does x += delta on its way
 

@@ -11,7 +11,9 @@ class TensorDecl:
     """One tensor a part reads, by its full name in the checkpoint.
 
     `init` says how the random-weights mode fills it: "normal" (N(0, std)),
-    "ones_normal" (1 + N(0, std), for norm weights) or "zeros".
+    "ones_normal" (1 + N(0, std), for norm weights), "zeros", "uniform" (evenly drawn
+    from `span` = (low, high), for constants that must stay in a range) or "eye_normal"
+    (the identity + N(0, std), for small square mixing matrices).
     `group`: tensors with the same group name, declared one after another,
     with equal trailing sizes and equal stored types, are laid back to back in
     device memory, so that the part can use them as one tensor (a fused
@@ -23,3 +25,4 @@ class TensorDecl:
     init: str = "normal"
     group: Optional[str] = None
     integer: bool = False
+    span: Optional[tuple] = None

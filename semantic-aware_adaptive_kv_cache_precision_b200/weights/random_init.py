@@ -34,10 +34,15 @@ def random_tensor(decl: TensorDecl, seed: int, std: float, dtype: torch.dtype) -
         return torch.from_numpy(rng.integers(0, 2 ** 15, size=shape, dtype=np.int32))
     if decl.init == "zeros":
         values = np.zeros(shape, dtype=np.float32)
+    elif decl.init == "uniform":
+        low, high = decl.span
+        values = rng.uniform(low, high, size=shape).astype(np.float32)
     else:
         values = rng.standard_normal(shape, dtype=np.float32) * np.float32(std)
         if decl.init == "ones_normal":
             values += np.float32(1.0)
+        elif decl.init == "eye_normal":
+            values += np.eye(*shape, dtype=np.float32)
     return torch.from_numpy(values).to(dtype)
 
 
@@ -88,6 +93,10 @@ def random_arena(decls: list[TensorDecl], seed: int, std: float, mode: str, devi
                                      dtype=torch.int32))
         elif d.init == "zeros":
             view.zero_()
+        elif d.init == "uniform":
+            low, high = d.span
+            view.copy_((torch.rand(view.shape, generator=gen, device=device,
+                                   dtype=torch.float32) * (high - low) + low).to(stored_dtype))
         else:
             chunk = 1 << 26
             flat = view.reshape(-1)
@@ -97,5 +106,8 @@ def random_arena(decls: list[TensorDecl], seed: int, std: float, mode: str, devi
                                     dtype=torch.float32) * std
                 if d.init == "ones_normal":
                     noise += 1.0
+                elif d.init == "eye_normal":       # (small matrices: one chunk)
+                    noise = (noise.view(view.shape)
+                             + torch.eye(*view.shape, device=device)).reshape(-1)
                 part.copy_(noise.to(stored_dtype))     # the value a checkpoint would store
     return arena
