@@ -355,8 +355,199 @@ def kernel_case(name: str) -> int:
     return 0
 
 
+#: layer sizes that resemble real models, for `--design tebonex`: (width, delta heads x dim,
+#: attention heads / kv heads x dim, window, feed-forward, vocabulary, streams, layers)
+DESIGN_SIZES = {
+    "1k": dict(width=1024, delta=(16, 64), attention=(8, 2, 128), window=512, ff=4096,
+               vocab=32768, streams=2, layers=6),
+    "2k": dict(width=2048, delta=(32, 64), attention=(16, 4, 128), window=1024, ff=8192,
+               vocab=32768, streams=2, layers=6),
+}
+
+
+def design_configs(size: dict) -> tuple:
+    """(Tebonex config, the Qwen2 config of equal width, depth, heads and feed-forward)."""
+    heads, kv_heads, dim = size["attention"]
+    layers = []
+    for i in range(size["layers"]):
+        if i % 3 == 2:
+            mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim,
+                     "scale": dim ** -0.5, "mask": {"size": size["window"]}}
+            kind = "attention"
+        else:
+            mixer = {"heads": size["delta"][0], "dim": size["delta"][1], "decay_rank": 64}
+            kind = "general_delta"
+        layers.append({"type": kind, "mixer": mixer, "mlp": {"kind": "dense", "ff": size["ff"]}})
+    tebonex = {"architecture": "Tebonex", "vocab": size["vocab"], "width": size["width"],
+               "streams": size["streams"], "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+               "initializer_range": 0.02, "layers": layers}
+    qwen2 = {**QWEN25_1P5B, "num_hidden_layers": size["layers"], "hidden_size": size["width"],
+             "num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": dim,
+             "intermediate_size": size["ff"], "vocab_size": size["vocab"],
+             "tie_word_embeddings": False}
+    return tebonex, qwen2
+
+
+def design_arm(args) -> int:
+    """`--design tebonex`: prefill and decode throughput of the Tebonex design at layer sizes
+    that resemble real models (random weights, bf16), beside the Qwen2 decoder of equal
+    width, depth and feed-forward size, and the time of every kernel of this library in a
+    Tebonex step (CUDA events around each launch of a step run kernel by kernel) with the
+    fraction of the measured peaks that the design's own kernels reach. One JSON line."""
+    import numpy as np
+    import torch
+    import semantic_aware_adaptive_kv_cache_precision_b200 as sakv
+    from semantic_aware_adaptive_kv_cache_precision_b200 import sampling
+    from semantic_aware_adaptive_kv_cache_precision_b200.ops import _lib
+
+    K, W, batch, context, tokens = args.steps, max(args.warmup, 3), args.batch, args.context, \
+        PREFILL_TOKENS
+    rng = np.random.default_rng(0)
+    pk = peaks()
+    hbm = pk.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"])
+    room = batch * (-(-(context + K + W + 8) // 64) * 64) + 64 * 64
+    greedy = sampling.SamplingParams()
+    sizes = [s for s in args.design_sizes.split(",") if s]
+    rows = []
+
+    def measure(config, graphs=True):
+        engine = sakv.Engine(config=config, dtype="bfloat16", random_seed=0, max_batch=batch,
+                             max_tokens=room, max_step_tokens=8192,
+                             cuda_graphs=graphs).load_weights()
+        vocab = engine.vocab_size
+        prompt = rng.integers(0, vocab, tokens)
+        times = []
+        for i in range(W + 5):
+            (slot,) = engine.open(1)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            sampling.choose(engine.step([slot], [prompt]), greedy)
+            b.record()
+            torch.cuda.synchronize()
+            engine.close([slot])
+            if i >= W:
+                times.append(a.elapsed_time(b))
+        prefill_ms = statistics.median(times)
+        slots = engine.open(batch)
+        for s in slots:
+            engine.step([s], [rng.integers(0, vocab, context)], [[]])
+        chosen = torch.as_tensor(rng.integers(0, vocab, batch), dtype=torch.int32).cuda()
+        for _ in range(W):
+            chosen = engine.next_tokens(slots, chosen)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        before = _lib.launches
+        a.record()
+        for _ in range(K):
+            chosen = engine.next_tokens(slots, chosen)
+        b.record()
+        torch.cuda.synchronize()
+        launched = _lib.launches - before
+        decode_ms = a.elapsed_time(b) / K
+        out = {"prefill_tok_s": round(tokens / prefill_ms * 1e3, 1), "prefill_ms": round(prefill_ms, 3),
+               "decode_tok_s": round(batch * 1e3 / decode_ms, 1), "decode_ms_per_step": round(decode_ms, 4),
+               "weight_mb": round(engine.model.weight_bytes / 1e6, 1), "launches_per_step": launched // K}
+        return engine, slots, prompt, out
+
+    def kernel_times(engine, slots, prompt):
+        """us of each kernel of this library in one prefill step and one decode step, run
+        kernel by kernel with an event on each side of every launch."""
+        real = _lib.function
+        log = []
+
+        def timed(name):
+            fn = real(name)
+
+            def run(*a):
+                x, y = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                x.record()
+                code = fn(*a)
+                y.record()
+                log.append((name, x, y))
+                return code
+            return run
+
+        out = {}
+        _lib.function = timed
+        try:
+            for what in ("prefill", "decode"):
+                for i in range(3):
+                    del log[:]
+                    if what == "prefill":
+                        (slot,) = engine.open(1)
+                        engine.step([slot], [prompt])
+                        engine.close([slot])
+                    else:
+                        engine.step(slots, [[1]] * len(slots))
+                    torch.cuda.synchronize()
+                total = {}
+                for name, x, y in log:
+                    total[name] = total.get(name, 0.0) + x.elapsed_time(y) * 1e3
+                out[what] = {k.replace("sakv_", ""): round(v, 1) for k, v in sorted(total.items())}
+        finally:
+            _lib.function = real
+        return out
+
+    for name in sizes:
+        size = DESIGN_SIZES[name]
+        tebonex, qwen2 = design_configs(size)
+        row = {"size": name, **{k: size[k] for k in ("width", "layers", "ff", "window", "streams")}}
+        for label, config in (("qwen2", qwen2), ("tebonex", tebonex)):
+            engine, slots, prompt, out = measure(config)
+            row[label] = out
+            engine.close(slots)
+            engine.release()
+            del engine
+            torch.cuda.empty_cache()
+        engine, slots, prompt, _ = measure(tebonex, graphs=False)
+        row["tebonex_kernels_us"] = times = kernel_times(engine, slots, prompt)
+        # what the design's own kernels must move or compute, against the measured peaks
+        n_delta = sum(1 for l in tebonex["layers"] if l["type"] == "general_delta")
+        n_att = size["layers"] - n_delta
+        dh, dd = size["delta"]
+        ah, ag, ad = size["attention"]
+        state_bytes = batch * dh * dd * dd * 4 * 2 * n_delta                    # read + write
+        kv_bytes = batch * min(context, size["window"]) * ag * ad * 2 * 2 * n_att
+        frac = {}
+        if times["decode"].get("delta_rule"):
+            frac["delta_rule_decode_of_measured_hbm"] = round(
+                state_bytes / (times["decode"]["delta_rule"] * 1e-6) / 1e9 / hbm, 3)
+        if times["decode"].get("distance_attention"):
+            frac["attention_decode_of_measured_hbm"] = round(
+                kv_bytes / (times["decode"]["distance_attention"] * 1e-6) / 1e9 / hbm, 3)
+        stream_bytes = tokens * size["width"] * 4 * (2 * size["streams"] + 2) * 2 * size["layers"]
+        if times["prefill"].get("streams_step"):
+            frac["streams_step_prefill_of_measured_hbm"] = round(
+                stream_bytes / (times["prefill"]["streams_step"] * 1e-6) / 1e9 / hbm, 3)
+        if times["prefill"].get("delta_rule"):     # 3 multiply-adds a state element a token
+            flops = 6.0 * tokens * dh * dd * dd * n_delta
+            frac["delta_rule_prefill_tflops_fp32"] = round(
+                flops / (times["prefill"]["delta_rule"] * 1e-6) / 1e12, 2)
+        if times["prefill"].get("distance_attention"):
+            keys = sum(min(i + 1, size["window"]) for i in range(tokens))
+            flops = 4.0 * ah * ad * keys * n_att
+            frac["attention_prefill_tflops_fp32"] = round(
+                flops / (times["prefill"]["distance_attention"] * 1e-6) / 1e12, 2)
+        row["tebonex_kernel_rates"] = frac
+        engine.close(slots)
+        engine.release()
+        del engine
+        torch.cuda.empty_cache()
+        rows.append(row)
+    print(json.dumps({"design": "tebonex", "beside": "qwen2 of equal width, depth, heads and "
+                      "feed-forward size", "dtype": "bf16", "data": "synthetic (random weights "
+                      "and tokens; weights larger than L2)", "batch": batch, "context": context,
+                      "prefill_tokens": tokens, "steps": K, "warmup": W, "peaks": pk,
+                      "sizes": rows}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--design", default=None, choices=["tebonex"],
+                    help="instead of the default workload: the named design at layer sizes "
+                         "that resemble real models, beside the Qwen2 decoder of equal size")
+    ap.add_argument("--design-sizes", default="1k,2k", help="which of: " + ", ".join(DESIGN_SIZES))
     ap.add_argument("--kernel", default=None,
                     help="run one kernel case for a profiler: gemm_gateup_b8, gemm_down_b8, "
                          "gemm_head_b8, gemm_gated_2048, attention_decode_b64, "
@@ -391,6 +582,8 @@ def main() -> int:
         args.warmup = 3
     if args.impl == "reference":
         return reference_arm(args)
+    if args.design:
+        return design_arm(args)
     import numpy as np
     import torch
     import semantic_aware_adaptive_kv_cache_precision_b200 as sakv

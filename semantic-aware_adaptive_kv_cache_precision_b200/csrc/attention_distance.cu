@@ -112,6 +112,289 @@ __global__ void distance_attention_kernel(
   }
 }
 
+// The faster form for key and value widths up to 256. A warp takes up to P query heads of one
+// token that share a key/value head and walks the visible keys in chunks of 32 positions
+// (aligned to multiples of 32, so a chunk lies in one cache block): each lane scores ONE key
+// against the P queries (the key's row is read once for all of them, the queries come from
+// shared memory), the chunk's maxima and sums are taken across the lanes, and for the
+// weighted sum of the values the lanes share out the value's columns while the weights go
+// round by shuffle. `splits` warps may share one token's keys (a decoded token has few
+// queries and many keys) and merge their running maxima, sums and partial outputs through
+// shared memory. With one warp a token the sums have the same terms in the same order
+// however the tokens are cut into steps.
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
+template <int P, int VPL, typename T>
+__global__ void __launch_bounds__(512)
+distance_attention_tiled_kernel(
+    const T* __restrict__ qkv, long long stride, int gate_off, T* __restrict__ out,
+    const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+    const int32_t* __restrict__ positions, const int32_t* __restrict__ token_seq,
+    const int32_t* __restrict__ block_table, int max_blocks, int tokens, int heads, int kv_heads,
+    int dim, int vdim, float scale, int window, const float* __restrict__ slope,
+    const float* __restrict__ rate, int splits, int row_floats) {
+  extern __shared__ float shared[];
+  let_next_kernel_start();
+  wait_for_previous_kernel();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const int hg = heads / kv_heads, per_group = (hg + P - 1) / P;
+  const long long items = (long long)tokens * kv_heads * per_group;
+  const long long item = (long long)blockIdx.x * (warps / splits) + warp / splits;
+  const int split = warp % splits;
+  const bool active = item < items;
+  float* mine = shared + (long long)warp * P * row_floats;     // queries now, partials later
+  int t = 0, g = 0, h0 = 0, np = 0, pos = 0, first = 0;
+  float m[P], l[P], acc[P][VPL], sl[P], rt[P];
+#pragma unroll
+  for (int p = 0; p < P; ++p) {
+    m[p] = -INFINITY;
+    l[p] = 0.f;
+    sl[p] = rt[p] = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) acc[p][i] = 0.f;
+  }
+  const bool wide_k = dim % 8 == 0 && !((uintptr_t)k_cache & 15);
+  const bool wide_v = vdim % VPL == 0 && lane * VPL + VPL <= vdim && !((uintptr_t)v_cache & 15);
+  if (active) {
+    t = static_cast<int>(item % tokens);
+    const int rest = static_cast<int>(item / tokens);
+    const int qi = rest % per_group;
+    g = rest / per_group;
+    h0 = g * hg + qi * P;
+    np = hg - qi * P < P ? hg - qi * P : P;
+    pos = positions[t];
+    first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+#pragma unroll
+    for (int p = 0; p < P; ++p) {
+      if (p < np && slope) {
+        sl[p] = slope[h0 + p];
+        rt[p] = rate[h0 + p];
+      }
+      for (int e = lane; e < dim; e += 32)
+        mine[p * row_floats + e] =
+            p < np ? widen(qkv[(long long)t * stride + (long long)(h0 + p) * dim + e]) : 0.f;
+    }
+    __syncwarp();
+    const int32_t* table = block_table + (long long)token_seq[t] * max_blocks;
+    for (int c = first / 32 + split; c <= pos / 32; c += splits) {
+      const int j = c * 32 + lane;
+      const bool valid = j >= first && j <= pos;
+      const long long rows = ((long long)table[c >> 1] * kv_heads + g) * kCacheBlock + (c & 1) * 32;
+      float s[P];
+#pragma unroll
+      for (int p = 0; p < P; ++p) s[p] = 0.f;
+      if (valid) {
+        const T* kp = k_cache + (rows + lane) * dim;
+        if (wide_k) {
+          for (int e = 0; e < dim; e += 8) {
+            float kv[8];
+            load8<T>(kp + e, kv);
+#pragma unroll
+            for (int p = 0; p < P; ++p) {
+              const float4 a = *reinterpret_cast<const float4*>(mine + p * row_floats + e);
+              const float4 b = *reinterpret_cast<const float4*>(mine + p * row_floats + e + 4);
+              s[p] = fmaf(a.x, kv[0], s[p]); s[p] = fmaf(a.y, kv[1], s[p]);
+              s[p] = fmaf(a.z, kv[2], s[p]); s[p] = fmaf(a.w, kv[3], s[p]);
+              s[p] = fmaf(b.x, kv[4], s[p]); s[p] = fmaf(b.y, kv[5], s[p]);
+              s[p] = fmaf(b.z, kv[6], s[p]); s[p] = fmaf(b.w, kv[7], s[p]);
+            }
+          }
+        } else {
+          for (int e = 0; e < dim; ++e) {
+            const float kv = widen(kp[e]);
+#pragma unroll
+            for (int p = 0; p < P; ++p) s[p] = fmaf(mine[p * row_floats + e], kv, s[p]);
+          }
+        }
+      }
+      const float dist = (float)(pos - j);
+      float w[P];
+#pragma unroll
+      for (int p = 0; p < P; ++p) {
+        float sc = -INFINITY;
+        if (valid) {
+          sc = s[p] * scale;
+          if (slope) sc -= sl[p] * log1pf(rt[p] * dist);
+        }
+        const float m_new = fmaxf(m[p], warp_max(sc));
+        const float corr = expf(m[p] - m_new);
+        w[p] = valid ? expf(sc - m_new) : 0.f;
+        l[p] = fmaf(l[p], corr, warp_sum(w[p]));
+        m[p] = m_new;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) acc[p][i] *= corr;
+      }
+      const int lo = first - c * 32 > 0 ? first - c * 32 : 0;
+      const int hi = pos - c * 32 < 31 ? pos - c * 32 : 31;
+      const T* vp = v_cache + rows * vdim + lane * VPL;
+      for (int kk = lo; kk <= hi; ++kk) {
+        float pk[P];
+#pragma unroll
+        for (int p = 0; p < P; ++p) pk[p] = __shfl_sync(0xffffffffu, w[p], kk);
+        const T* vr = vp + (long long)kk * vdim;
+        if (wide_v) {                    // a lane's columns in one access
+          alignas(16) T got[VPL];
+          constexpr int kBytes = VPL * (int)sizeof(T);
+          if constexpr (kBytes == 32) {
+            reinterpret_cast<uint4*>(got)[0] = reinterpret_cast<const uint4*>(vr)[0];
+            reinterpret_cast<uint4*>(got)[1] = reinterpret_cast<const uint4*>(vr)[1];
+          } else if constexpr (kBytes == 16) {
+            *reinterpret_cast<uint4*>(got) = *reinterpret_cast<const uint4*>(vr);
+          } else if constexpr (kBytes == 8) {
+            *reinterpret_cast<uint2*>(got) = *reinterpret_cast<const uint2*>(vr);
+          } else if constexpr (kBytes == 4) {
+            *reinterpret_cast<uint32_t*>(got) = *reinterpret_cast<const uint32_t*>(vr);
+          } else {
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) got[i] = vr[i];
+          }
+#pragma unroll
+          for (int i = 0; i < VPL; ++i) {
+            const float v = widen(got[i]);
+#pragma unroll
+            for (int p = 0; p < P; ++p) acc[p][i] = fmaf(pk[p], v, acc[p][i]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < VPL; ++i) {
+            if (lane * VPL + i < vdim) {
+              const float v = widen(vr[i]);
+#pragma unroll
+              for (int p = 0; p < P; ++p) acc[p][i] = fmaf(pk[p], v, acc[p][i]);
+            }
+          }
+        }
+      }
+    }
+  }
+  if (splits > 1) {                      // (uniform over the block)
+    __syncwarp();
+    if (active) {
+#pragma unroll
+      for (int p = 0; p < P; ++p) {
+        float* row = mine + p * row_floats;
+        if (lane == 0) {
+          row[0] = m[p];
+          row[1] = l[p];
+        }
+#pragma unroll
+        for (int i = 0; i < VPL; ++i)
+          if (lane * VPL + i < vdim) row[2 + lane * VPL + i] = acc[p][i];
+      }
+    }
+    __syncthreads();
+    if (!active || split != 0) return;
+#pragma unroll
+    for (int p = 0; p < P; ++p) {
+      float top = -INFINITY;
+      for (int w = 0; w < splits; ++w)
+        top = fmaxf(top, shared[((long long)(warp + w) * P + p) * row_floats]);
+      float total = 0.f, sum[VPL];
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) sum[i] = 0.f;
+      for (int w = 0; w < splits; ++w) {
+        const float* row = shared + ((long long)(warp + w) * P + p) * row_floats;
+        const float f = expf(row[0] - top);
+        total = fmaf(row[1], f, total);
+#pragma unroll
+        for (int i = 0; i < VPL; ++i)
+          if (lane * VPL + i < vdim) sum[i] = fmaf(row[2 + lane * VPL + i], f, sum[i]);
+      }
+      l[p] = total;
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) acc[p][i] = sum[i];
+    }
+  }
+  if (!active) return;
+#pragma unroll
+  for (int p = 0; p < P; ++p) {
+    if (p >= np) continue;
+    float gate = 1.f;
+    if (gate_off >= 0) {
+      const float z = widen(qkv[(long long)t * stride + gate_off + h0 + p]);
+      gate = 1.f / (1.f + expf(-z));
+    }
+    const float inv = gate / l[p];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i)
+      if (lane * VPL + i < vdim)
+        out[((long long)t * heads + h0 + p) * vdim + lane * VPL + i] = narrow<T>(acc[p][i] * inv);
+  }
+}
+
+template <int P, int VPL, typename T>
+int launch_tiled(const void* qkv, long long stride, int gate_off, void* out, const void* k_cache,
+                 const void* v_cache, const int32_t* positions, const int32_t* token_seq,
+                 const int32_t* block_table, int max_blocks, int tokens, int heads, int kv_heads,
+                 int dim, int vdim, float scale, int window, const float* slope,
+                 const float* rate, int splits, cudaStream_t stream) {
+  constexpr int kBudget = 96 * 1024;
+  static PerDeviceOnce configured;
+  auto kernel = distance_attention_tiled_kernel<P, VPL, T>;
+  if (configured.needs()) {
+    const cudaError_t e =
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBudget);
+    if (e != cudaSuccess) return (int)e;
+    configured.done();
+  }
+  const int hg = heads / kv_heads, per_group = (hg + P - 1) / P;
+  int row_floats = (dim > vdim + 2 ? dim : vdim + 2);
+  row_floats = (row_floats + 3) / 4 * 4;                     // rows stay 16-byte aligned
+  int warps = splits > 1 ? splits : 4;
+  while ((size_t)warps * P * row_floats * sizeof(float) > (size_t)kBudget && warps > 1) warps /= 2;
+  if ((size_t)warps * P * row_floats * sizeof(float) > (size_t)kBudget) return cudaErrorInvalidValue;
+  if (splits > 1) splits = warps;
+  const long long items = (long long)tokens * kv_heads * per_group;
+  const long long blocks = (items + warps / splits - 1) / (warps / splits);
+  if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
+  return launch_overlapped(kernel, dim3((unsigned)blocks), dim3(warps * 32),
+                           (size_t)warps * P * row_floats * sizeof(float), stream, 1,
+                           (const T*)qkv, stride, gate_off, (T*)out, (const T*)k_cache,
+                           (const T*)v_cache, positions, token_seq, block_table, max_blocks,
+                           tokens, heads, kv_heads, dim, vdim, scale, window, slope, rate, splits,
+                           row_floats);
+}
+
+template <typename T>
+int pick_tiled(const void* qkv, long long stride, int gate_off, void* out, const void* k_cache,
+               const void* v_cache, const int32_t* positions, const int32_t* token_seq,
+               const int32_t* block_table, int max_blocks, int tokens, int heads, int kv_heads,
+               int dim, int vdim, float scale, int window, const float* slope, const float* rate,
+               int splits, cudaStream_t stream) {
+  const int hg = heads / kv_heads;
+#define SAKV_TILED(P, VPL)                                                                       \
+  return launch_tiled<P, VPL, T>(qkv, stride, gate_off, out, k_cache, v_cache, positions,        \
+                                 token_seq, block_table, max_blocks, tokens, heads, kv_heads, dim, \
+                                 vdim, scale, window, slope, rate, splits, stream)
+#define SAKV_TILED_P(VPL)          \
+  if (hg == 1) SAKV_TILED(1, VPL); \
+  if (hg == 2) SAKV_TILED(2, VPL); \
+  SAKV_TILED(4, VPL)
+  if (vdim <= 32) { SAKV_TILED_P(1); }
+  if (vdim <= 64) { SAKV_TILED_P(2); }
+  if (vdim <= 128) { SAKV_TILED_P(4); }
+  SAKV_TILED_P(8);
+#undef SAKV_TILED_P
+#undef SAKV_TILED
+}
+
 template <typename T>
 int launch_attention(const void* qkv, long long stride, int gate_off, void* out,
                      const void* k_cache, const void* v_cache, const int32_t* positions,
@@ -163,17 +446,31 @@ SAKV_EXPORT int sakv_kv_store(const void* qkv, int dtype, long long stride, int 
 // qkv: [tokens, stride] with the queries in its first heads * dim columns and, if gate_off
 // >= 0, the gates' pre-activations in columns gate_off .. gate_off + heads - 1. slope, rate:
 // fp32 [heads] (null: no penalty). window 0: every earlier key. out: [tokens, heads * vdim].
+// `splits`: 0 runs the plain form (a warp for each token and head, one key at a time); 1 the
+// form that scores 32 keys at a time (widths up to 256); more than 1 lets that many warps
+// (up to 16) share a token's keys.
 SAKV_EXPORT int sakv_distance_attention(const void* qkv, int dtype, long long stride, int gate_off,
                                         void* out, const void* k_cache, const void* v_cache,
                                         const int32_t* positions, const int32_t* token_seq,
                                         const int32_t* block_table, int max_blocks, int tokens,
                                         int heads, int kv_heads, int dim, int vdim, float scale,
                                         int window, const float* slope, const float* rate,
-                                        cudaStream_t stream) {
+                                        int splits, cudaStream_t stream) {
   if (tokens < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || vdim <= 0 ||
-      dim > 512 || vdim > 512 || max_blocks <= 0 || window < 0)
+      dim > 512 || vdim > 512 || max_blocks <= 0 || window < 0 || splits < 0 || splits > 16)
     return cudaErrorInvalidValue;
   if (tokens == 0) return 0;
+  if (splits > 0 && dim <= 256 && vdim <= 256) {
+    if (dtype == SAKV_F32)
+      return pick_tiled<float>(qkv, stride, gate_off, out, k_cache, v_cache, positions, token_seq,
+                               block_table, max_blocks, tokens, heads, kv_heads, dim, vdim, scale,
+                               window, slope, rate, splits, stream);
+    if (dtype == SAKV_BF16)
+      return pick_tiled<__nv_bfloat16>(qkv, stride, gate_off, out, k_cache, v_cache, positions,
+                                       token_seq, block_table, max_blocks, tokens, heads, kv_heads,
+                                       dim, vdim, scale, window, slope, rate, splits, stream);
+    return cudaErrorInvalidValue;
+  }
   if (dtype == SAKV_F32)
     return launch_attention<float>(qkv, stride, gate_off, out, k_cache, v_cache, positions,
                                    token_seq, block_table, max_blocks, tokens, heads, kv_heads,

@@ -178,11 +178,16 @@ def distance_attention(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                        positions: torch.Tensor, token_seq: torch.Tensor,
                        block_table: torch.Tensor, heads: int, scale: float, window: int | None,
                        slope: torch.Tensor | None, rate: torch.Tensor | None,
-                       gate_off: int | None = None) -> torch.Tensor:
+                       gate_off: int | None = None, splits: int = 1) -> torch.Tensor:
     """Causal grouped-query attention of every token of the step over its sequence's cache
     with the score `q.k * scale - slope[h] * ln(1 + rate[h] * distance)`; queries are the first
     heads * dim columns of `qkv`, and with `gate_off` each head's output is multiplied by
-    `sigmoid(qkv[:, gate_off + h])`. Returns [T, heads * vdim] of qkv's type."""
+    `sigmoid(qkv[:, gate_off + h])`. Returns [T, heads * vdim] of qkv's type.
+
+    `splits`: 1 (the default) scores 32 keys at a time with one warp for a token's heads of a
+    key/value head, and gives a token the same result to the bit however the tokens come; more
+    (up to 16) lets that many warps share a token's keys, for steps of few tokens over many
+    keys; 0 is the plain form, one key at a time, which also takes widths above 256."""
     require_cuda(qkv, k_cache, v_cache, positions, token_seq, block_table, slope, rate)
     tokens = qkv.shape[0]
     kv_heads, dim, vdim = k_cache.shape[1], k_cache.shape[3], v_cache.shape[3]
@@ -202,7 +207,8 @@ def distance_attention(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     call("sakv_distance_attention", ptr(qkv), dtype_code(qkv.dtype), qkv.stride(0),
          -1 if gate_off is None else int(gate_off), ptr(out), ptr(k_cache), ptr(v_cache),
          ptr(positions), ptr(token_seq), ptr(block_table), block_table.shape[1], tokens, heads,
-         kv_heads, dim, vdim, float(scale), int(window) if window else 0, ptr(slope), ptr(rate))
+         kv_heads, dim, vdim, float(scale), int(window) if window else 0, ptr(slope), ptr(rate),
+         int(splits))
     return out
 
 

@@ -39,5 +39,6 @@ def delta_rule(proj: torch.Tensor, offsets: tuple, w2: torch.Tensor, w0: torch.T
     call("sakv_delta_rule", ptr(proj), proj.stride(0), *[int(o) for o in offsets], ptr(w2),
          ptr(w0), ptr(a_bias), ptr(norm_w), dtype_code(w2.dtype), ptr(state),
          ptr(step.cu_seqlens), ptr(step.slots), ptr(out), dtype_code(out_dtype), step.sequences,
-         heads, dim, rank, float(decay_scale), float(key_eps), float(eps), int(keep_state))
+         heads, dim, rank, int(max(1, min(64, getattr(step, "max_new", 0) or tokens))),
+         float(decay_scale), float(key_eps), float(eps), int(keep_state))
     return out

@@ -84,8 +84,24 @@ class LogDistanceAttention(Part):
         attended = ops.distance_attention(
             qkv, view.keys, view.values, step.positions, step.token_seq, view.block_table,
             s.heads, s.scale, s.window, self.slope, self.rate,
-            gate_off=self.q_cols + self.k_cols + self.v_cols if s.head_gate else None)
+            gate_off=self.q_cols + self.k_cols + self.v_cols if s.head_gate else None,
+            splits=self._splits(step, qkv))
         return ops.linear(attended, self.w_o, self.b_o, out_dtype=torch.float32)
+
+    def _splits(self, step, qkv) -> int:
+        """How many warps share a token's keys. One in the 32-bit mode and for prompts (the
+        sums then have one order however the tokens are cut); for decode steps in bfloat16 one
+        warp for every two chunks of 32 keys that a token can see, up to 16. (A decode
+        step's graph is keyed by the width of the block lists, which bounds the length.)"""
+        if qkv.dtype == torch.float32 or not step.is_decode:
+            return 1
+        keys = step.max_len_bound or step.max_len
+        if self.spec.window:
+            keys = min(keys, self.spec.window + 31)
+        splits = 1
+        while splits < 16 and splits * 64 < keys:
+            splits *= 2
+        return splits
 
     def forward(self, h, step, view, residual, write_cache=True):
         ops.add_into(residual, self.produce(h, step, view, write_cache))

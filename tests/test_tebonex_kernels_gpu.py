@@ -182,7 +182,8 @@ def attention_plain(q64, heads, kv_heads, dim, vdim, scale, slope, rate, window)
     return out.reshape(n, heads * vdim)
 
 
-def run_attention(qkv, pieces, heads, kv_heads, dim, vdim, scale, slope, rate, window, blocks):
+def run_attention(qkv, pieces, heads, kv_heads, dim, vdim, scale, slope, rate, window, blocks,
+                  splits=1):
     """The tokens of one sequence in `pieces`, through a cache whose blocks are `blocks`."""
     k_cache = torch.full((8, kv_heads, 64, dim), float("nan"), dtype=qkv.dtype, device=DEV)
     v_cache = torch.full((8, kv_heads, 64, vdim), float("nan"), dtype=qkv.dtype, device=DEV)
@@ -195,7 +196,8 @@ def run_attention(qkv, pieces, heads, kv_heads, dim, vdim, scale, slope, rate, w
                      table, k_cache, v_cache)
         out.append(ops.distance_attention(rows, k_cache, v_cache, step.positions, step.token_seq,
                                           table, heads, scale, window, dev(slope), dev(rate),
-                                          gate_off=(heads + kv_heads) * dim + kv_heads * vdim))
+                                          gate_off=(heads + kv_heads) * dim + kv_heads * vdim,
+                                          splits=splits))
         at += n
     return torch.cat(out).float().cpu().numpy()
 
@@ -219,6 +221,15 @@ def test_distance_attention_in_a_prompt_in_pieces_and_decoded(heads, kv_heads, d
     cut = run_attention(qkv, [2, 61, 1, 1, 64, 3] + [1] * 68, heads, kv_heads, dim, vdim, 0.2,
                         slope32, rate32, window, blocks)
     assert np.array_equal(cut, whole)
+    # the plain form (a key at a time) and warps that share a token's keys: the same numbers
+    # within rounding, and each of them the same to the bit however the tokens are cut
+    for splits in (0, 2, 16):
+        other = run_attention(qkv, [n], heads, kv_heads, dim, vdim, 0.2, slope32, rate32, window,
+                              blocks, splits)
+        assert np.abs(other - want).max() <= tol * np.abs(want).max(), splits
+        again = run_attention(qkv, [150] + [1] * 50, heads, kv_heads, dim, vdim, 0.2, slope32,
+                              rate32, window, blocks, splits)
+        assert np.array_equal(again, other), splits
 
 
 @pytest.mark.parametrize("window", [1, 2, 63, 64, 65, 72, 128])
@@ -239,9 +250,10 @@ def test_a_key_that_stands_out_just_inside_and_just_outside_the_window(window):
         qkv = dev(base)
         slope = rate = np.zeros(1, dtype=np.float32)
         inside, outside = at + window - 1, at + window
-        for pieces in ([n], [at + 1] + [1] * (n - at - 1)):
+        for pieces, splits in (([n], 1), ([at + 1] + [1] * (n - at - 1), 1), ([n], 0),
+                               ([at + 1] + [1] * (n - at - 1), 4)):
             out = run_attention(qkv, pieces, heads, kv_heads, dim, vdim, 1.0, slope, rate, window,
-                                [3, 1, 6, 4, 0])
+                                [3, 1, 6, 4, 0], splits)
             marked = np.arange(1, vdim + 1)
             assert np.abs(out[inside] - marked).max() < 1e-2, (window, at, "inside")
             assert np.abs(out[outside]).max() < 0.5, (window, at, "outside")
