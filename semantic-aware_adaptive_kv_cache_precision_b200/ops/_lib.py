@@ -29,8 +29,8 @@ SIGNATURES = {
     "sakv_streams_step": ("streams", [P, L, I, I, I, P, P, P, I, P, P, I, F, P, I, P]),
     "sakv_token_shift": ("streams", [P, P, P, I, P, P, P, P, I, I, I, I, P]),
     "sakv_streams_spread": ("streams", [P, L, I, L, P]),
-    "sakv_delta_rule": ("delta_rule", [P, L, I, I, I, I, I, I, P, P, P, P, I, P, P, P, P, I,
-                                       I, I, I, I, I, F, F, F, I, P]),
+    "sakv_delta_rule": ("delta_rule", [P, L, I, I, I, I, I, I, P, P, P, P, I, P, P, P, P, P, P,
+                                       I, I, I, I, I, I, I, F, F, F, I, P]),
     "sakv_kv_store": ("attention_distance", [P, I, L, I, I, P, P, P, I, P, P, I, I, I, I, P]),
     "sakv_distance_attention": ("attention_distance",
                                 [P, I, L, I, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, P, I, P]),

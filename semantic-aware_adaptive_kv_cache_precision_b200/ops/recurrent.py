@@ -36,9 +36,12 @@ def delta_rule(proj: torch.Tensor, offsets: tuple, w2: torch.Tensor, w0: torch.T
     check(state.dtype == torch.float32 and state.is_contiguous()
           and tuple(state.shape[1:]) == (heads, dim, dim), "state: fp32 [slots, heads, dim, dim]")
     out = torch.empty((tokens, hd), dtype=out_dtype, device=proj.device)
+    prepared = torch.empty((tokens, 3, hd), dtype=torch.float32, device=proj.device)
+    raw = torch.empty((tokens, hd), dtype=torch.float32, device=proj.device)
     call("sakv_delta_rule", ptr(proj), proj.stride(0), *[int(o) for o in offsets], ptr(w2),
-         ptr(w0), ptr(a_bias), ptr(norm_w), dtype_code(w2.dtype), ptr(state),
-         ptr(step.cu_seqlens), ptr(step.slots), ptr(out), dtype_code(out_dtype), step.sequences,
-         heads, dim, rank, int(max(1, min(64, getattr(step, "max_new", 0) or tokens))),
+         ptr(w0), ptr(a_bias), ptr(norm_w), dtype_code(w2.dtype), ptr(prepared), ptr(raw), ptr(state),
+         ptr(step.cu_seqlens), ptr(step.slots), ptr(out), dtype_code(out_dtype), tokens,
+         step.sequences, heads, dim, rank,
+         int(max(1, min(16, getattr(step, "max_new", 0) or tokens))),
          float(decay_scale), float(key_eps), float(eps), int(keep_state))
     return out
