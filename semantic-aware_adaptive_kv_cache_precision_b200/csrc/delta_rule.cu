@@ -129,37 +129,57 @@ delta_scan_kernel(const float* __restrict__ proj, long long proj_stride, int off
     const int count = min(chunk, end - t0);
     float* dst = shared + buffer * per_buffer;
     float* dst_v = dst + chunk * 5 * ldt;
+    // (an item is four floats, or one, of one of the six vectors; its place in the token is
+    // worked out once, then it is copied for every token of the chunk)
     if (aligned) {
       const int quads = dim / 4, vquads = cols / 4, per_token = 5 * quads + vquads;
-      for (int i = tid; i < count * per_token; i += threads) {
-        const int tt = i / per_token, rest = i - tt * per_token;
-        const long long t = t0 + tt;
-        if (rest >= 5 * quads) {
-          const int c = (rest - 5 * quads) * 4;
-          copy16_async(dst_v + tt * cols + c, proj + t * proj_stride + off_v + base + col0 + c);
+      for (int j = tid; j < per_token; j += threads) {
+        const float* src;
+        float* to;
+        long long src_step = proj_stride;
+        int to_step = 5 * ldt;
+        if (j >= 5 * quads) {
+          const int c = (j - 5 * quads) * 4;
+          src = proj + (long long)t0 * proj_stride + off_v + base + col0 + c;
+          to = dst_v + c;
+          to_step = cols;
         } else {
-          const int which = rest / quads, c = (rest - which * quads) * 4;
-          const float* src = which == 0 ? proj + t * proj_stride + off_r + base + c
-                           : which == 1 ? proj + t * proj_stride + off_k + base + c
-                                        : prepared + (t * 3 + (which - 2)) * hd + base + c;
-          copy16_async(dst + (tt * 5 + which) * ldt + (c / rpt) * ldp + c % rpt, src);
+          const int which = j / quads, c = (j - which * quads) * 4;
+          to = dst + which * ldt + (c / rpt) * ldp + c % rpt;
+          if (which < 2) {
+            src = proj + (long long)t0 * proj_stride + (which == 0 ? off_r : off_k) + base + c;
+          } else {
+            src = prepared + ((long long)t0 * 3 + (which - 2)) * hd + base + c;
+            src_step = 3 * hd;
+          }
         }
+        for (int tt = 0; tt < count; ++tt) copy16_async(to + tt * to_step, src + tt * src_step);
       }
     } else {
       const int per_token = 5 * dim + cols;
-      for (int i = tid; i < count * per_token; i += threads) {
-        const int tt = i / per_token, rest = i - tt * per_token;
-        const long long t = t0 + tt;
-        if (rest >= 5 * dim) {
-          const int c = rest - 5 * dim;
-          dst_v[tt * cols + c] = col0 + c < dim ? proj[t * proj_stride + off_v + base + col0 + c] : 0.f;
+      for (int j = tid; j < per_token; j += threads) {
+        const float* src;
+        float* to;
+        long long src_step = proj_stride;
+        int to_step = 5 * ldt;
+        bool real = true;
+        if (j >= 5 * dim) {
+          const int c = j - 5 * dim;
+          real = col0 + c < dim;
+          src = proj + (long long)t0 * proj_stride + off_v + base + col0 + c;
+          to = dst_v + c;
+          to_step = cols;
         } else {
-          const int which = rest / dim, c = rest - which * dim;
-          dst[(tt * 5 + which) * ldt + (c / rpt) * ldp + c % rpt] =
-              which == 0 ? proj[t * proj_stride + off_r + base + c]
-            : which == 1 ? proj[t * proj_stride + off_k + base + c]
-                         : prepared[(t * 3 + (which - 2)) * hd + base + c];
+          const int which = j / dim, c = j - which * dim;
+          to = dst + which * ldt + (c / rpt) * ldp + c % rpt;
+          if (which < 2) {
+            src = proj + (long long)t0 * proj_stride + (which == 0 ? off_r : off_k) + base + c;
+          } else {
+            src = prepared + ((long long)t0 * 3 + (which - 2)) * hd + base + c;
+            src_step = 3 * hd;
+          }
         }
+        for (int tt = 0; tt < count; ++tt) to[tt * to_step] = real ? src[tt * src_step] : 0.f;
       }
     }
     copies_commit();
@@ -297,20 +317,13 @@ int pick_scan(const float* proj, long long proj_stride, const int* off, const fl
     int lanes = 4;
     while (lanes < 16 && dim % (8 * lanes) == 0 && dim / (2 * lanes) >= 8) lanes *= 2;
     const int rpt = dim / lanes;
-    if (lanes == 4) {
-      if (rpt <= 4) SAKV_SCAN(4, 4, true);
-      if (rpt <= 8) SAKV_SCAN(8, 4, true);
-      if (rpt <= 16) SAKV_SCAN(16, 4, true);
-      if (rpt <= 32) SAKV_SCAN(32, 4, true);
-      SAKV_SCAN(64, 4, true);
-    }
-    if (lanes == 8) {
-      if (rpt <= 8) SAKV_SCAN(8, 8, true);
-      if (rpt <= 16) SAKV_SCAN(16, 8, true);
-      SAKV_SCAN(32, 8, true);
-    }
-    if (rpt <= 8) SAKV_SCAN(8, 16, true);
-    SAKV_SCAN(16, 16, true);
+    if (lanes == 4 && rpt <= 4) SAKV_SCAN(4, 4, true);
+    if (lanes == 4 && rpt <= 8) SAKV_SCAN(8, 4, true);
+    if (lanes == 4 && rpt <= 16) SAKV_SCAN(16, 4, true);
+    if (lanes == 8 && rpt <= 8) SAKV_SCAN(8, 8, true);
+    if (lanes == 8 && rpt <= 16) SAKV_SCAN(16, 8, true);
+    if (lanes == 16 && rpt <= 8) SAKV_SCAN(8, 16, true);
+    if (lanes == 16 && rpt <= 16) SAKV_SCAN(16, 16, true);
   }
   if (dim <= 32) SAKV_SCAN(32, 1, false);
   if (dim <= 64) SAKV_SCAN(64, 1, false);
