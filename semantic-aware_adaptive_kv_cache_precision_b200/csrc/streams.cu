@@ -28,7 +28,10 @@ __global__ void __launch_bounds__(kThreads)
 streams_step_kernel(float* __restrict__ xs, long long stream_stride, int streams, int width,
                     const float* __restrict__ y, const W* __restrict__ mix,
                     const W* __restrict__ out_w, int reduce, const W* __restrict__ in_w,
-                    const W* __restrict__ norm_w, float eps, Out* __restrict__ out) {
+                    const W* __restrict__ norm_w, float eps, Out* __restrict__ out,
+                    float* __restrict__ shift_state, const W* __restrict__ shift_w,
+                    const int32_t* __restrict__ token_seq, const int32_t* __restrict__ slots,
+                    int keep_state) {
   extern __shared__ float u_row[];                 // [width]
   __shared__ float scratch[33];
   __shared__ float c_mix[S * S], c_out[S], c_in[S];
@@ -83,9 +86,20 @@ streams_step_kernel(float* __restrict__ xs, long long stream_stride, int streams
     r = 1.f / sqrtf(total / (float)width + eps);
   }
   Out* o = out + row * width;
+  // With `shift_state` every row is the one token its sequence brings in this step: the blend
+  // with the token before (`token_shift` below) happens here, on the normed row.
+  float* kept = shift_state ? shift_state + (long long)slots[token_seq[row]] * width : nullptr;
   // (each thread reads back the columns it wrote itself)
-  for (int c = threadIdx.x; c < width; c += kThreads)
-    o[c] = narrow<Out>(norm_w ? u_row[c] * r * widen(norm_w[c]) : u_row[c]);
+  for (int c = threadIdx.x; c < width; c += kThreads) {
+    const float cur = norm_w ? u_row[c] * r * widen(norm_w[c]) : u_row[c];
+    if (kept) {
+      const float prev = kept[c];
+      if (keep_state) kept[c] = cur;
+      o[c] = narrow<Out>(fmaf(prev - cur, widen(shift_w[c]), cur));
+    } else {
+      o[c] = narrow<Out>(cur);
+    }
+  }
 }
 
 template <typename W, typename Out>
@@ -131,7 +145,9 @@ __global__ void streams_spread_kernel(float* __restrict__ xs, long long stream_s
 template <int S, typename W>
 int launch_step(float* xs, long long stride, int streams, int tokens, int width, const float* y,
                 const void* mix, const void* out_w, int reduce, const void* in_w,
-                const void* norm_w, float eps, void* out, int out_dtype, cudaStream_t stream) {
+                const void* norm_w, float eps, void* out, int out_dtype, float* shift_state,
+                const void* shift_w, const int32_t* token_seq, const int32_t* slots,
+                int keep_state, cudaStream_t stream) {
   const size_t smem = reduce ? (size_t)width * sizeof(float) : 0;
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
   auto go = [&](auto kernel, auto* o) {
@@ -142,7 +158,8 @@ int launch_step(float* xs, long long stride, int streams, int tokens, int width,
     }
     return launch_overlapped(kernel, dim3(tokens), dim3(kThreads), smem, stream, 1, xs, stride,
                              streams, width, y, (const W*)mix, (const W*)out_w, reduce,
-                             (const W*)in_w, (const W*)norm_w, eps, o);
+                             (const W*)in_w, (const W*)norm_w, eps, o, shift_state,
+                             (const W*)shift_w, token_seq, slots, keep_state);
   };
   if (out_dtype == SAKV_F32) return go(streams_step_kernel<S, W, float>, (float*)out);
   if (out_dtype == SAKV_BF16) return go(streams_step_kernel<S, W, __nv_bfloat16>, (__nv_bfloat16*)out);
@@ -152,10 +169,13 @@ int launch_step(float* xs, long long stride, int streams, int tokens, int width,
 template <typename W>
 int pick_step(float* xs, long long stride, int streams, int tokens, int width, const float* y,
               const void* mix, const void* out_w, int reduce, const void* in_w,
-              const void* norm_w, float eps, void* out, int out_dtype, cudaStream_t stream) {
+              const void* norm_w, float eps, void* out, int out_dtype, float* shift_state,
+              const void* shift_w, const int32_t* token_seq, const int32_t* slots,
+              int keep_state, cudaStream_t stream) {
 #define SAKV_STEP(S)                                                                          \
   return launch_step<S, W>(xs, stride, streams, tokens, width, y, mix, out_w, reduce, in_w,   \
-                           norm_w, eps, out, out_dtype, stream)
+                           norm_w, eps, out, out_dtype, shift_state, shift_w, token_seq, slots, \
+                           keep_state, stream)
   if (streams == 1) SAKV_STEP(1);
   if (streams == 2) SAKV_STEP(2);
   if (streams <= 4) SAKV_STEP(4);
@@ -170,21 +190,28 @@ int pick_step(float* xs, long long stride, int streams, int tokens, int width, c
 // null): [tokens, width] fp32 to write back with `mix` [streams, streams] (from, to) and
 // `out_w` [streams] (null: identity and ones). `reduce` != 0: out[tokens, width] = the
 // normed weighted sum (`in_w` null: ones; `norm_w` null: no norm, out must be fp32-sized
-// for its type all the same). The constants are of type `w_dtype`.
+// for its type all the same). The constants are of type `w_dtype`. `shift_state` (or null):
+// fp32 [slots, width]; given only when every row is the one token that its sequence
+// (`token_seq`, `slots`) brings, it blends the result with the sequence's row before, as
+// `sakv_token_shift` does, and leaves the unblended result there.
 SAKV_EXPORT int sakv_streams_step(float* xs, long long stream_stride, int streams, int tokens,
                                   int width, const float* y, const void* mix, const void* out_w,
                                   int reduce, const void* in_w, const void* norm_w, int w_dtype,
-                                  float eps, void* out, int out_dtype, cudaStream_t stream) {
+                                  float eps, void* out, int out_dtype, float* shift_state,
+                                  const void* shift_w, const int32_t* token_seq,
+                                  const int32_t* slots, int keep_state, cudaStream_t stream) {
   if (streams < 1 || streams > 16 || tokens < 0 || width <= 0 || (!y && !reduce) ||
-      (reduce && !out))
+      (reduce && !out) || (shift_state && (!reduce || !shift_w || !token_seq || !slots)))
     return cudaErrorInvalidValue;
   if (tokens == 0) return 0;
   if (w_dtype == SAKV_F32)
     return pick_step<float>(xs, stream_stride, streams, tokens, width, y, mix, out_w, reduce,
-                            in_w, norm_w, eps, out, out_dtype, stream);
+                            in_w, norm_w, eps, out, out_dtype, shift_state, shift_w, token_seq,
+                            slots, keep_state, stream);
   if (w_dtype == SAKV_BF16)
     return pick_step<__nv_bfloat16>(xs, stream_stride, streams, tokens, width, y, mix, out_w,
-                                    reduce, in_w, norm_w, eps, out, out_dtype, stream);
+                                    reduce, in_w, norm_w, eps, out, out_dtype, shift_state,
+                                    shift_w, token_seq, slots, keep_state, stream);
   return cudaErrorInvalidValue;
 }
 

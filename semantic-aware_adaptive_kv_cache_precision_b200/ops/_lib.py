@@ -26,7 +26,8 @@ SIGNATURES = {
     "sakv_add_into": ("elementwise", [P, P, I, L, P]),
     "sakv_scale_cap": ("elementwise", [P, L, F, F, P]),
     "sakv_gelu_tanh": ("elementwise", [P, P, I, L, P]),
-    "sakv_streams_step": ("streams", [P, L, I, I, I, P, P, P, I, P, P, I, F, P, I, P]),
+    "sakv_streams_step": ("streams", [P, L, I, I, I, P, P, P, I, P, P, I, F, P, I, P, P, P, P, I,
+                                      P]),
     "sakv_token_shift": ("streams", [P, P, P, I, P, P, P, P, I, I, I, I, P]),
     "sakv_streams_spread": ("streams", [P, L, I, L, P]),
     "sakv_delta_rule": ("delta_rule", [P, L, I, I, I, I, I, I, P, P, P, P, I, P, P, P, P, P, P,

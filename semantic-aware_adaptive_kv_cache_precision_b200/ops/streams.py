@@ -26,11 +26,16 @@ def streams_step(xs: torch.Tensor, *, y: torch.Tensor | None = None,
                  mix: torch.Tensor | None = None, out_w: torch.Tensor | None = None,
                  reduce: bool = True, in_w: torch.Tensor | None = None,
                  norm_w: torch.Tensor | None = None, eps: float = 0.0,
-                 out_dtype: torch.dtype = torch.float32) -> torch.Tensor | None:
+                 out_dtype: torch.dtype = torch.float32, shift: tuple | None = None,
+                 keep_state: bool = True) -> torch.Tensor | None:
     """On `xs` (fp32 [streams, T, width], updated in place): with `y` (fp32 [T, width]) first
     `xs[t] <- sum_s mix[s, t] xs[s] + out_w[t] y` (`mix` None: the identity, `out_w` None:
     ones); then, with `reduce`, returns `norm(sum_s in_w[s] xs[s])` as [T, width] of
-    `out_dtype` (`in_w` None: ones; `norm_w` None: the sum itself, fp32)."""
+    `out_dtype` (`in_w` None: ones; `norm_w` None: the sum itself, fp32).
+
+    `shift` = (state, shift_w, step), only for a step in which every sequence brings ONE token:
+    the result is blended with the sequence's row before as `token_shift` does, in the same
+    kernel, and `state` receives the unblended rows."""
     require_cuda(xs, y)
     _check(xs.dtype == torch.float32 and xs.dim() == 3 and xs[0].is_contiguous(),
            "xs: fp32 [streams, T, width] with contiguous streams")
@@ -43,7 +48,16 @@ def streams_step(xs: torch.Tensor, *, y: torch.Tensor | None = None,
         _check(out_w is None or out_w.shape == (streams,), "out_w: [streams]")
     _check(in_w is None or in_w.shape == (streams,), "in_w: [streams]")
     _check(norm_w is None or norm_w.shape == (width,), "norm_w: [width]")
-    code = _constants(mix, out_w, in_w, norm_w)
+    state = shift_w = step = None
+    if shift is not None:
+        state, shift_w, step = shift
+        require_cuda(state, shift_w)
+        _check(reduce and norm_w is not None, "a shift needs the normed result")
+        _check(state.dtype == torch.float32 and state.dim() == 2 and state.shape[1] == width
+               and state.is_contiguous(), "state: contiguous fp32 [slots, width]")
+        _check(shift_w.shape == (width,) and step.sequences == tokens,
+               "shift_w: [width]; a shift inside the step needs one token a sequence")
+    code = _constants(mix, out_w, in_w, norm_w, shift_w)
     out = None
     if reduce:
         if norm_w is None:
@@ -51,7 +65,9 @@ def streams_step(xs: torch.Tensor, *, y: torch.Tensor | None = None,
         out = torch.empty((tokens, width), dtype=out_dtype, device=xs.device)
     call("sakv_streams_step", ptr(xs), xs.stride(0), streams, tokens, width, ptr(y), ptr(mix),
          ptr(out_w), int(reduce), ptr(in_w), ptr(norm_w), code, float(eps), ptr(out),
-         dtype_code(out.dtype) if out is not None else 0)
+         dtype_code(out.dtype) if out is not None else 0, ptr(state), ptr(shift_w),
+         ptr(step.token_seq) if step is not None else None,
+         ptr(step.slots) if step is not None else None, int(keep_state))
     return out
 
 

@@ -112,12 +112,17 @@ class StreamBlock(Part):
         mixer_view, shift_view = (view.parts if s.token_shift else (view, None))
         w_in, w_mix, w_out = self.hc[1]
         norm = self.mixer_norm
+        # one token a sequence: the blend with the token before is part of the same kernel
+        inside = s.token_shift and step.is_decode
         h = ops.streams_step(
             xs, y=None if pending is None else pending.y,
             mix=None if pending is None else pending.mix,
             out_w=None if pending is None else pending.out_w, in_w=w_in, norm_w=norm.weight,
-            eps=norm.spec.eps, out_dtype=torch.float32 if s.token_shift else self.act_dtype)
-        if s.token_shift:
+            eps=norm.spec.eps,
+            out_dtype=torch.float32 if s.token_shift and not inside else self.act_dtype,
+            shift=(shift_view.state, self.shift, step) if inside else None,
+            keep_state=write_cache)
+        if s.token_shift and not inside:
             h = ops.token_shift(h, shift_view.state, self.shift, step, self.act_dtype,
                                 keep_state=write_cache)
         update = StreamUpdate(self._run(self.mixer, h, step, mixer_view, write_cache),

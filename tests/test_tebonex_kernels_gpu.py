@@ -81,6 +81,25 @@ def test_token_shift_takes_the_row_before_from_the_state_and_leaves_the_last():
     assert float(state[5].min()) == 99.0
 
 
+def test_the_shift_inside_the_streams_step_is_the_shift_after_it():
+    """One token a sequence: norm and blend in one kernel give the bits of the two kernels."""
+    rng = np.random.default_rng(2)
+    streams, width, eps = 3, 70, 1e-6
+    xs = dev(rng.standard_normal((streams, 4, width)))
+    in_w, norm_w, shift = dev(rng.uniform(0.2, 0.8, streams)), dev(1 + 0.1 * rng.standard_normal(width)), \
+        dev(rng.uniform(0, 1, width))
+    kept = dev(rng.standard_normal((9, width)))
+    step = step_of([1, 1, 1, 1], [8, 0, 3, 5], [4, 0, 9, 2])
+    state_a, state_b = kept.clone(), kept.clone()
+    h = ops.streams_step(xs, in_w=in_w, norm_w=norm_w, eps=eps)
+    two = ops.token_shift(h, state_a, shift, step, torch.float32)
+    one = ops.streams_step(xs, in_w=in_w, norm_w=norm_w, eps=eps, shift=(state_b, shift, step))
+    assert torch.equal(one, two) and torch.equal(state_a, state_b)
+    assert torch.equal(state_a[[8, 0, 3, 5]], h) and torch.equal(state_a[1], kept[1])
+    want = h + (kept[[8, 0, 3, 5]] - h) * shift
+    assert float((one - want).abs().max()) <= 1e-6 * float(want.abs().max())
+
+
 def delta_inputs(rng, n, heads, dim, rank, w0, a_bias):
     hd = heads * dim
     proj = rng.standard_normal((n, 5 * hd + rank)).astype(np.float32)
