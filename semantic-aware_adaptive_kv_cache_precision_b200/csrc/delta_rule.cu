@@ -338,13 +338,14 @@ int run(const float* proj, long long proj_stride, const int* off, const void* w2
         const int32_t* cu_seqlens, const int32_t* slots, void* out, int out_dtype, int tokens,
         int sequences, int heads, int dim, int rank, int chunk, float decay_scale, float key_eps,
         float eps, int keep_state, cudaStream_t stream) {
+  constexpr size_t kPrepareBudget = 200 * 1024;
   const size_t smem = ((size_t)dim * (rank + 1) + (size_t)kPrepareTokens * rank) * sizeof(float);
-  if (smem > kScanBudget) return cudaErrorInvalidValue;
+  if (smem > kPrepareBudget) return cudaErrorInvalidValue;
   static PerDeviceOnce configured;
   if (configured.needs()) {
     const cudaError_t e = cudaFuncSetAttribute(delta_prepare_kernel<W>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)kScanBudget);
+                                               (int)kPrepareBudget);
     if (e != cudaSuccess) return (int)e;
     configured.done();
   }

@@ -26,7 +26,10 @@ from pathlib import Path
 
 import numpy as np
 
+from ..cache import BLOCK
 from .engine import Engine
+
+SLACK_REQUESTS = 256
 
 
 class TraceError(ValueError):
@@ -99,9 +102,11 @@ def main(argv=None) -> int:
                         help="bfloat16: the serving kernels; float32: everything in true 32-bit")
     parser.add_argument("--out", required=True, help="folder for <step>.f32 files")
     parser.add_argument("--max-tokens", type=int, required=True,
-                        help="most tokens that live requests hold at any time, each request "
-                             "rounded up to a multiple of 64; sizes the cache")
+                        help="most tokens that live requests hold at any time; sizes the cache")
     args = parser.parse_args(argv)
-    engine = Engine(args.model, dtype=args.dtype, max_tokens=args.max_tokens).load_weights()
+    # the cache counts a request in blocks of 64 positions: room for the last, partly filled
+    # block of each of up to SLACK_REQUESTS live requests is added to what was asked for
+    engine = Engine(args.model, dtype=args.dtype,
+                    max_tokens=args.max_tokens + SLACK_REQUESTS * BLOCK).load_weights()
     Replayer(engine, args.out).run(sys.stdin)
     return 0

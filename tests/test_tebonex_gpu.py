@@ -173,3 +173,22 @@ def test_the_replay_program_runs_a_tebonex_folder(dtype, folders, tmp_path):
         got = trace.send([entry("a", a[t:t + 1], [0])], end=["a"] if t == 89 else [])
         assert_close_to_plain(got, want["a"][t:t + 1], dtype, f"a alone at {t}")
     trace.finish()
+
+
+def test_the_command_line_writes_and_runs_a_tebonex_folder(tmp_path):
+    """`random-model` from a config.json, then `generate` and `throughput` on the folder."""
+    import json
+    from test_cli import run
+    config = tmp_path / "config.json"
+    config.write_text(json.dumps(CONFIGS["single"][0]))
+    run("random-model", "--config", str(config), "--seed", "3", "--out", str(tmp_path / "m"),
+        "--stored-dtype", "float32")
+    cfg, tensors = plain.read_model_folder(tmp_path / "m")
+    assert cfg["architecture"] == "Tebonex" and tensors["l1.mix.r1"].shape == (8,)
+    (p,) = prompts_of("single", (11,), seed=7)
+    records, _ = run("generate", "--model", str(tmp_path / "m"), "--dtype", "float32",
+                     "--ignore-eos", "--prompt-ids", ",".join(map(str, p)), "--new-tokens", "6")
+    assert records[0]["tokens"] == plain.generate(cfg, tensors, p.tolist(), 6)
+    records, _ = run("throughput", "--model", str(tmp_path / "m"), "--lengths", "70",
+                     "--repeat", "1", "--warmup", "1", "--batch", "2")
+    assert records[0]["decode_tokens_per_second"] > 0

@@ -122,7 +122,8 @@ def delta_plain(proj, c, heads, dim, eps, state=None):
 
 
 @pytest.mark.parametrize("heads,dim,rank", [(3, 16, 8), (1, 64, 16), (2, 48, 5), (5, 8, 1),
-                                            (2, 128, 3), (1, 136, 2)])
+                                            (2, 128, 3), (1, 136, 2), (2, 32, 70), (1, 256, 100),
+                                            (3, 80, 4), (7, 20, 9)])
 def test_delta_rule_whole_in_pieces_and_beside_another_sequence(heads, dim, rank):
     rng = np.random.default_rng(dim)
     n, eps = 75, 1e-5
@@ -224,7 +225,8 @@ def run_attention(qkv, pieces, heads, kv_heads, dim, vdim, scale, slope, rate, w
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim,window",
                          [(4, 2, 16, 24, 37), (1, 1, 64, 64, 64), (3, 1, 8, 8, 1), (2, 2, 32, 16, None),
-                          (8, 4, 16, 32, 130), (2, 1, 72, 40, 65), (1, 1, 160, 264, 5)])
+                          (8, 4, 16, 32, 130), (2, 1, 72, 40, 65), (1, 1, 160, 264, 5),
+                          (6, 1, 20, 12, 40), (5, 5, 128, 256, 70), (12, 2, 8, 200, None)])
 def test_distance_attention_in_a_prompt_in_pieces_and_decoded(heads, kv_heads, dim, vdim, window, dtype):
     rng = np.random.default_rng(dim + vdim)
     n = 200
