@@ -203,17 +203,26 @@ distance_attention_tiled_kernel(
       if (valid) {
         const T* kp = k_cache + (rows + lane) * dim;
         if (wide_k) {
-          for (int e = 0; e < dim; e += 8) {
-            float kv[8];
-            load8<T>(kp + e, kv);
+          // four 16-byte pieces of the key's row are asked for before any is used
+          for (int e = 0; e < dim; e += 32) {
+            float kv[4][8];
 #pragma unroll
-            for (int p = 0; p < P; ++p) {
-              const float4 a = *reinterpret_cast<const float4*>(mine + p * row_floats + e);
-              const float4 b = *reinterpret_cast<const float4*>(mine + p * row_floats + e + 4);
-              s[p] = fmaf(a.x, kv[0], s[p]); s[p] = fmaf(a.y, kv[1], s[p]);
-              s[p] = fmaf(a.z, kv[2], s[p]); s[p] = fmaf(a.w, kv[3], s[p]);
-              s[p] = fmaf(b.x, kv[4], s[p]); s[p] = fmaf(b.y, kv[5], s[p]);
-              s[p] = fmaf(b.z, kv[6], s[p]); s[p] = fmaf(b.w, kv[7], s[p]);
+            for (int i = 0; i < 4; ++i)
+              if (e + 8 * i < dim) load8<T>(kp + e + 8 * i, kv[i]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              if (e + 8 * i < dim) {
+#pragma unroll
+                for (int p = 0; p < P; ++p) {
+                  const float* q = mine + p * row_floats + e + 8 * i;
+                  const float4 a = *reinterpret_cast<const float4*>(q);
+                  const float4 b = *reinterpret_cast<const float4*>(q + 4);
+                  s[p] = fmaf(a.x, kv[i][0], s[p]); s[p] = fmaf(a.y, kv[i][1], s[p]);
+                  s[p] = fmaf(a.z, kv[i][2], s[p]); s[p] = fmaf(a.w, kv[i][3], s[p]);
+                  s[p] = fmaf(b.x, kv[i][4], s[p]); s[p] = fmaf(b.y, kv[i][5], s[p]);
+                  s[p] = fmaf(b.z, kv[i][6], s[p]); s[p] = fmaf(b.w, kv[i][7], s[p]);
+                }
+              }
             }
           }
         } else {
@@ -244,41 +253,44 @@ distance_attention_tiled_kernel(
       const int lo = first - c * 32 > 0 ? first - c * 32 : 0;
       const int hi = pos - c * 32 < 31 ? pos - c * 32 : 31;
       const T* vp = v_cache + rows * vdim + lane * VPL;
-      for (int kk = lo; kk <= hi; ++kk) {
-        float pk[P];
+      for (int k0 = lo; k0 <= hi; k0 += 4) {         // four values' rows in flight at a time
+        alignas(16) T got[4][VPL];
 #pragma unroll
-        for (int p = 0; p < P; ++p) pk[p] = __shfl_sync(0xffffffffu, w[p], kk);
-        const T* vr = vp + (long long)kk * vdim;
-        if (wide_v) {                    // a lane's columns in one access
-          alignas(16) T got[VPL];
-          constexpr int kBytes = VPL * (int)sizeof(T);
-          if constexpr (kBytes == 32) {
-            reinterpret_cast<uint4*>(got)[0] = reinterpret_cast<const uint4*>(vr)[0];
-            reinterpret_cast<uint4*>(got)[1] = reinterpret_cast<const uint4*>(vr)[1];
-          } else if constexpr (kBytes == 16) {
-            *reinterpret_cast<uint4*>(got) = *reinterpret_cast<const uint4*>(vr);
-          } else if constexpr (kBytes == 8) {
-            *reinterpret_cast<uint2*>(got) = *reinterpret_cast<const uint2*>(vr);
-          } else if constexpr (kBytes == 4) {
-            *reinterpret_cast<uint32_t*>(got) = *reinterpret_cast<const uint32_t*>(vr);
+        for (int n = 0; n < 4; ++n) {
+          const T* vr = vp + (long long)(k0 + n) * vdim;
+          if (k0 + n > hi) continue;
+          if (wide_v) {                    // a lane's columns in one access
+            constexpr int kBytes = VPL * (int)sizeof(T);
+            if constexpr (kBytes == 32) {
+              reinterpret_cast<uint4*>(got[n])[0] = reinterpret_cast<const uint4*>(vr)[0];
+              reinterpret_cast<uint4*>(got[n])[1] = reinterpret_cast<const uint4*>(vr)[1];
+            } else if constexpr (kBytes == 16) {
+              *reinterpret_cast<uint4*>(got[n]) = *reinterpret_cast<const uint4*>(vr);
+            } else if constexpr (kBytes == 8) {
+              *reinterpret_cast<uint2*>(got[n]) = *reinterpret_cast<const uint2*>(vr);
+            } else if constexpr (kBytes == 4) {
+              *reinterpret_cast<uint32_t*>(got[n]) = *reinterpret_cast<const uint32_t*>(vr);
+            } else {
+#pragma unroll
+              for (int i = 0; i < VPL; ++i) got[n][i] = vr[i];
+            }
           } else {
 #pragma unroll
-            for (int i = 0; i < VPL; ++i) got[i] = vr[i];
+            for (int i = 0; i < VPL; ++i)
+              got[n][i] = lane * VPL + i < vdim ? vr[i] : narrow<T>(0.f);
           }
+        }
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+          if (k0 + n > hi) continue;
+          float pk[P];
+#pragma unroll
+          for (int p = 0; p < P; ++p) pk[p] = __shfl_sync(0xffffffffu, w[p], k0 + n);
 #pragma unroll
           for (int i = 0; i < VPL; ++i) {
-            const float v = widen(got[i]);
+            const float v = widen(got[n][i]);
 #pragma unroll
             for (int p = 0; p < P; ++p) acc[p][i] = fmaf(pk[p], v, acc[p][i]);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < VPL; ++i) {
-            if (lane * VPL + i < vdim) {
-              const float v = widen(vr[i]);
-#pragma unroll
-              for (int p = 0; p < P; ++p) acc[p][i] = fmaf(pk[p], v, acc[p][i]);
-            }
           }
         }
       }
