@@ -122,6 +122,15 @@ __global__ void distance_attention_kernel(
 // queries and many keys) and merge their running maxima, sums and partial outputs through
 // shared memory. With one warp a token the sums have the same terms in the same order
 // however the tokens are cut into steps.
+__device__ __forceinline__ void copy16_async(void* dst, const void* src) {
+  const uint32_t to = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(to), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copies_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void copies_wait_all_but_last() {
+  asm volatile("cp.async.wait_group 1;" ::: "memory");
+}
+
 template <typename T>
 __device__ __forceinline__ void load8(const T* p, float (&v)[8]);
 template <>
@@ -149,8 +158,8 @@ distance_attention_tiled_kernel(
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_seq,
     const int32_t* __restrict__ block_table, int max_blocks, int tokens, int heads, int kv_heads,
     int dim, int vdim, float scale, int window, const float* __restrict__ slope,
-    const float* __restrict__ rate, int splits, int row_floats) {
-  extern __shared__ float shared[];
+    const float* __restrict__ rate, int splits, int row_floats, int stage_ok) {
+  extern __shared__ __align__(16) float shared[];
   let_next_kernel_start();
   wait_for_previous_kernel();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
@@ -172,6 +181,21 @@ distance_attention_tiled_kernel(
   }
   const bool wide_k = dim % 8 == 0 && !((uintptr_t)k_cache & 15);
   const bool wide_v = vdim % VPL == 0 && lane * VPL + VPL <= vdim && !((uintptr_t)v_cache & 15);
+  // (the same for every thread of the block)
+  bool staged = false;
+  int block_first = 0, block_last = 0;
+  if (stage_ok && splits == 1) {
+    const long long item0 = (long long)blockIdx.x * warps, last = item0 + warps - 1;
+    if (last < items && item0 / tokens == last / tokens) {
+      const int t0 = static_cast<int>(item0 % tokens), t1 = t0 + warps - 1;
+      if (token_seq[t0] == token_seq[t1] && positions[t1] == positions[t0] + warps - 1) {
+        staged = true;
+        const int p0 = positions[t0];
+        block_first = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
+        block_last = positions[t1];
+      }
+    }
+  }
   if (active) {
     t = static_cast<int>(item % tokens);
     const int rest = static_cast<int>(item / tokens);
@@ -193,15 +217,15 @@ distance_attention_tiled_kernel(
     }
     __syncwarp();
     const int32_t* table = block_table + (long long)token_seq[t] * max_blocks;
-    for (int c = first / 32 + split; c <= pos / 32; c += splits) {
+    // chunk c: `kp` this lane's key's row, `vp` the chunk's first value row at this lane's
+    // columns, rows `vstride` apart (in the cache, or in the block's copy of the chunk)
+    auto chunk = [&](int c, const T* kp, const T* vp, int vstride) {
       const int j = c * 32 + lane;
       const bool valid = j >= first && j <= pos;
-      const long long rows = ((long long)table[c >> 1] * kv_heads + g) * kCacheBlock + (c & 1) * 32;
       float s[P];
 #pragma unroll
       for (int p = 0; p < P; ++p) s[p] = 0.f;
       if (valid) {
-        const T* kp = k_cache + (rows + lane) * dim;
         if (wide_k) {
           // four 16-byte pieces of the key's row are asked for before any is used
           for (int e = 0; e < dim; e += 32) {
@@ -252,12 +276,11 @@ distance_attention_tiled_kernel(
       }
       const int lo = first - c * 32 > 0 ? first - c * 32 : 0;
       const int hi = pos - c * 32 < 31 ? pos - c * 32 : 31;
-      const T* vp = v_cache + rows * vdim + lane * VPL;
       for (int k0 = lo; k0 <= hi; k0 += 4) {         // four values' rows in flight at a time
         alignas(16) T got[4][VPL];
 #pragma unroll
         for (int n = 0; n < 4; ++n) {
-          const T* vr = vp + (long long)(k0 + n) * vdim;
+          const T* vr = vp + (long long)(k0 + n) * vstride;
           if (k0 + n > hi) continue;
           if (wide_v) {                    // a lane's columns in one access
             constexpr int kBytes = VPL * (int)sizeof(T);
@@ -293,6 +316,52 @@ distance_attention_tiled_kernel(
             for (int p = 0; p < P; ++p) acc[p][i] = fmaf(pk[p], v, acc[p][i]);
           }
         }
+      }
+    };
+    auto rows_of = [&](int c) {
+      return ((long long)table[c >> 1] * kv_heads + g) * kCacheBlock + (c & 1) * 32;
+    };
+    if (!staged) {
+      for (int c = first / 32 + split; c <= pos / 32; c += splits) {
+        const long long rows = rows_of(c);
+        chunk(c, k_cache + (rows + lane) * dim, v_cache + rows * vdim + lane * VPL, vdim);
+      }
+    } else {
+      // The block's four tokens follow one another in one sequence and see nearly the same
+      // keys: every chunk is copied into shared memory once, a chunk ahead of its use, and
+      // each warp scores the chunks of its own token's range from there.
+      constexpr int kPiece = 16 / (int)sizeof(T);
+      const int kstride = dim + kPiece;              // padded: the lanes' rows hit different banks
+      T* stage = reinterpret_cast<T*>(shared + (long long)warps * P * row_floats);
+      const int per_buffer = 32 * (kstride + vdim);
+      const int c_lo = block_first / 32, c_hi = block_last / 32;
+      auto fetch = [&](int c, int buffer) {
+        const long long rows = rows_of(c);
+        T* ks = stage + buffer * per_buffer;
+        T* vs = ks + 32 * kstride;
+        const int kp16 = dim / kPiece, vp16 = vdim / kPiece;
+        for (int i = threadIdx.x; i < 32 * kp16; i += blockDim.x) {
+          const int r = i / kp16, q = (i - r * kp16) * kPiece;
+          copy16_async(ks + r * kstride + q, k_cache + (rows + r) * dim + q);
+        }
+        for (int i = threadIdx.x; i < 32 * vp16; i += blockDim.x) {
+          const int r = i / vp16, q = (i - r * vp16) * kPiece;
+          copy16_async(vs + r * vdim + q, v_cache + (rows + r) * vdim + q);
+        }
+        copies_commit();
+      };
+      fetch(c_lo, 0);
+      int buffer = 0;
+      for (int c = c_lo; c <= c_hi; ++c, buffer ^= 1) {
+        if (c < c_hi) fetch(c + 1, buffer ^ 1);
+        else copies_commit();
+        copies_wait_all_but_last();
+        __syncthreads();
+        if (c >= first / 32 && c <= pos / 32) {
+          const T* ks = stage + buffer * per_buffer;
+          chunk(c, ks + lane * kstride, ks + 32 * kstride + lane * VPL, vdim);
+        }
+        __syncthreads();
       }
     }
   }
@@ -369,19 +438,26 @@ int launch_tiled(const void* qkv, long long stride, int gate_off, void* out, con
   const int hg = heads / kv_heads, per_group = (hg + P - 1) / P;
   int row_floats = (dim > vdim + 2 ? dim : vdim + 2);
   row_floats = (row_floats + 3) / 4 * 4;                     // rows stay 16-byte aligned
-  int warps = splits > 1 ? splits : 4;
+  int warps = splits > 1 ? splits : (tokens >= 64 ? 8 : 4);     // (a block's tokens share keys)
   while ((size_t)warps * P * row_floats * sizeof(float) > (size_t)kBudget && warps > 1) warps /= 2;
   if ((size_t)warps * P * row_floats * sizeof(float) > (size_t)kBudget) return cudaErrorInvalidValue;
   if (splits > 1) splits = warps;
+  // prompts: room for two chunks of keys and values that a block's tokens share
+  size_t smem = (size_t)warps * P * row_floats * sizeof(float);
+  const size_t staging = (size_t)2 * 32 * (dim + 16 / sizeof(T) + vdim) * sizeof(T);
+  const int stage_ok = splits == 1 && warps >= 4 && tokens >= warps &&
+                       (dim * sizeof(T)) % 16 == 0 && (vdim * sizeof(T)) % 16 == 0 &&
+                       !((uintptr_t)k_cache & 15) && !((uintptr_t)v_cache & 15) &&
+                       smem + staging <= (size_t)kBudget;
+  if (stage_ok) smem += staging;
   const long long items = (long long)tokens * kv_heads * per_group;
   const long long blocks = (items + warps / splits - 1) / (warps / splits);
   if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
-  return launch_overlapped(kernel, dim3((unsigned)blocks), dim3(warps * 32),
-                           (size_t)warps * P * row_floats * sizeof(float), stream, 1,
+  return launch_overlapped(kernel, dim3((unsigned)blocks), dim3(warps * 32), smem, stream, 1,
                            (const T*)qkv, stride, gate_off, (T*)out, (const T*)k_cache,
                            (const T*)v_cache, positions, token_seq, block_table, max_blocks,
                            tokens, heads, kv_heads, dim, vdim, scale, window, slope, rate, splits,
-                           row_floats);
+                           row_floats, stage_ok);
 }
 
 template <typename T>
