@@ -28,4 +28,12 @@ PLAIN = {"architecture": "Tebonex", "vocab": 150, "width": 64,
 SINGLE = {"architecture": "Tebonex", "vocab": 97, "width": 128, "streams": 1,
           "embedding": {"scale": 3.0}, "norm": {"eps": 3e-6}, "initializer_range": 0.06,
           "layers": [delta(4, 32, 4, 200), attention(8, 4, 16, 32, 0.25, 130, 136)]}
-CONFIGS = {"mixed": (MIXED, 11), "plain": (PLAIN, 12), "single": (SINGLE, 13)}
+# sizes that no vector access divides: a width of 100, heads of 24 and 40, four streams.
+# (Its seed is one whose first tokens are well conditioned: after one token a head's state is
+# k v^T, so its normed output is v / rms(v) times the SIGN of r.k, and a seed that draws r.k
+# next to zero for some token turns rounding into a flipped sign, in any implementation.)
+ODD = {"architecture": "Tebonex", "vocab": 131, "width": 100, "streams": 4,
+       "embedding": {"scale": 9.0}, "norm": {"eps": 1e-5}, "initializer_range": 0.09,
+       "layers": [delta(5, 24, 7, 50), attention(5, 5, 24, 40, 0.2, 3, 90),
+                  attention(6, 2, 12, 20, 0.3, 100, None), delta(1, 100, 2, 33)]}
+CONFIGS = {"mixed": (MIXED, 11), "plain": (PLAIN, 12), "single": (SINGLE, 13), "odd": (ODD, 15)}
