@@ -25,8 +25,9 @@ class ConfigError(ValueError):
 
 @dataclass(frozen=True)
 class NormSpec:
-    """`suffix` is what the norm's weight is called after the norm's own name
-    (".weight" in most checkpoints, nothing in some)."""
+    """`kind` "rms_norm": x / sqrt(mean(x^2) + eps) * w; "layer_norm": (x - mean) /
+    sqrt(variance + eps) * w, no bias. `suffix` is what the norm's weight is called after
+    the norm's own name (".weight" in most checkpoints, nothing in some)."""
     size: int
     eps: float
     kind: str = "rms_norm"
@@ -34,13 +35,29 @@ class NormSpec:
 
 
 @dataclass(frozen=True)
+class RampScaling:
+    """Stretching of a rotation's long wavelengths for contexts beyond the one a model was
+    trained on (the YaRN scheme): a pair whose wavelength makes fewer than `slow` turns in
+    `original` positions has its frequency divided by `factor`, one that makes more than
+    `fast` turns keeps it, and a linear ramp over the pair index lies between. Cosines and
+    sines are all multiplied by `magnitude_slope * ln(factor) + 1`."""
+    factor: float
+    original: float
+    fast: float
+    slow: float
+    magnitude_slope: float = 0.1
+
+
+@dataclass(frozen=True)
 class RotarySpec:
-    """Rotate-half rotary position encoding of the first `rotary_dim` of each head."""
+    """Rotate-half rotary position encoding of the first `rotary_dim` of each head;
+    `scaling` (a `RampScaling`) stretches its long wavelengths."""
     head_dim: int
     rotary_dim: int
     theta: float
     max_positions: int
     kind: str = "rotary_half"
+    scaling: Optional[RampScaling] = None
 
 
 @dataclass(frozen=True)
@@ -123,6 +140,93 @@ class DeltaRuleSpec:
 
 
 @dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal attention whose keys and values are made from one cached latent a position.
+
+    The input is projected down to `kv_rank + rot_dim` numbers: the first `kv_rank`, divided
+    by their root mean square and multiplied by a weight, are the latent c; the last
+    `rot_dim`, rotated by the position, are a key part that all heads share. Head h's key
+    is [Wuk_h c | rotated part], its value Wuv_h c; its query [`head_dim` plain | `rot_dim`
+    rotated] comes from a query latent of `q_rank` numbers (normed like c; None: straight
+    from the input). The cache holds c and the rotated part only. `position.rotary_dim`
+    must be `rot_dim`.
+
+    Tensor names after the part's prefix: `dq`, `dq.norm`, `uq` (or `q` without a query
+    latent), `dkv`, `dkv.norm`, `uk`, `uv`, `o`."""
+    hidden: int
+    heads: int
+    head_dim: int
+    rot_dim: int
+    value_dim: int
+    kv_rank: int
+    q_rank: Optional[int]
+    scale: float
+    eps: float
+    position: RotarySpec
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class DifferentialAttentionSpec:
+    """Grouped-query causal attention with two softmax maps a head over the same values:
+
+        o = a1 - lam * a2,  lam = exp(lq1 . lk1) - exp(lq2 . lk2) + diff  (one number a layer)
+        out = o / sqrt(mean(o^2) + eps) * (1 - diff)              (over a head's values)
+
+    Queries are laid out head by head as [map 1 | map 2], each `head_dim` wide, keys
+    likewise a key/value head. No rotation. `chunk` c: query i sees key j <= i only if both
+    lie in the same run of c positions counted from the sequence's start (None: every
+    earlier key). `gate`: the concatenated heads are multiplied element by element with
+    `sigmoid(Wg x)` before the output projection.
+
+    Tensor names after the part's prefix: `q`, `k`, `v`, `g`, `o`, `lq1`, `lk1`, `lq2`, `lk2`."""
+    hidden: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    chunk: Optional[int]
+    diff: float
+    eps: float
+    gate: bool = True
+    kind: str = "differential_attention"
+
+
+@dataclass(frozen=True)
+class ClampedExpertSpec:
+    """A gated feed-forward with clamped branches: g = min(Wgate x, limit), u = clamp(Wup x,
+    -limit, limit), y = g * sigmoid(alpha * g) * (u + 1), out = Wdown y."""
+    intermediate: int
+    limit: float
+    alpha: float = 1.702
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec:
+    """A mixture of `experts` small feed-forwards (`e0`, `e1`, ...; all of form `expert`) of
+    which each token uses the `top` with the largest router scores. `score` "sigmoid":
+    each expert's score is the sigmoid of its router logit (fp32). `renormalize`: whether
+    the chosen scores are divided by their sum. `weight_input`: the score multiplies the
+    expert's input (out = sum expert(w x)) rather than its output. `shared`: one more
+    expert that every token uses, multiplied by `sigmoid(Wsg x)`, one number a token
+    (`shared.sg`), if `shared_gate`.
+
+    Tensor names after the part's prefix: `router`, `e<i>.gate`, `e<i>.up`, `e<i>.down`,
+    `shared.gate`, `shared.up`, `shared.down`, `shared.sg`."""
+    hidden: int
+    experts: int
+    top: int
+    expert: ClampedExpertSpec
+    shared: Optional[ClampedExpertSpec] = None
+    shared_gate: bool = True
+    score: str = "sigmoid"
+    renormalize: bool = False
+    weight_input: bool = True
+    kind: str = "routed_experts"
+
+
+@dataclass(frozen=True)
 class DenseMLPSpec:
     """Dense feed-forward without a gate: `down(act(up(x)))`; tensors `up` and `down`."""
     hidden: int
@@ -180,6 +284,23 @@ class StreamBlockSpec:
 
 
 @dataclass(frozen=True)
+class SandwichBlockSpec:
+    """A layer with a norm before AND after each sublayer:
+
+        x += norm1b(mixer(norm1(x)));   x += norm2b(ffn(norm2(x)))
+
+    `ffn` None: the layer has no feed-forward (and no `norm2`, `norm2b`)."""
+    prefix: str
+    mixer: object
+    ffn: object
+    norm: NormSpec
+    mixer_name: str = "mix"
+    ffn_name: str = "mlp"
+    norm_names: tuple = ("norm1", "norm1b", "norm2", "norm2b")
+    kind: str = "sandwich_block"
+
+
+@dataclass(frozen=True)
 class LayerCall:
     """One entry of the run order: run block `block` with cache entry `cache`.
 
@@ -188,9 +309,15 @@ class LayerCall:
     layer's cache). A block may appear in several calls (a layer run twice);
     each such call needs a cache entry of its own unless it shares one on
     purpose.
+
+    `mix_input`: before this call the stream is replaced by `W [x; x0]`, x0 being the
+    embedding's output and W the model's `ModelSpec.input_mix_name` ([hidden, 2 hidden],
+    the stream's columns first): how a run of layers that is repeated takes the input up
+    again at the start of every pass.
     """
     block: int
     cache: int
+    mix_input: bool = False
 
 
 @dataclass(frozen=True)
@@ -221,6 +348,7 @@ class ModelSpec:
     head_bias_name: Optional[str] = None
     ignore_tensors: tuple = ()
     streams: int = 1
+    input_mix_name: Optional[str] = None
 
     def cache_entries(self) -> int:
         return 1 + max((c.cache for c in self.run_order), default=-1)

@@ -12,9 +12,56 @@
 // beside other sequences. `kv_store` puts a step's keys and values (columns of the fused
 // projection's output) into the cache blocks: keys [block, kv_head, 64, dim], values
 // [block, kv_head, 64, vdim].
+//
+// The tiled form also takes what other kinds of cached attention need (`AttentionExtra`):
+//   * queries in two pieces from two tensors (a head's first columns from one projection, the
+//     rest from another), and heads that lie further apart than their width;
+//   * key rows and value rows wider than what a head reads of them, and values that ARE the
+//     first columns of the key rows (attention over one cached latent a position);
+//   * a mask of chunks instead of a sliding window: query i sees key j <= i only if both lie
+//     in the same run of `chunk` positions counted from the sequence's start;
+//   * several softmax maps a head over the same values (MAPS = 2: the key row holds one key
+//     a map, queries lie head by head as [map 1 | map 2]) combined as
+//       o = a1 - lambda * a2;  out = o / sqrt(mean(o^2) + eps) * out_scale * sigmoid(gate)
+//     with the gate taken element by element from the projection's output.
 #include "common.cuh"
 
+// What the tiled kernel needs beyond the plain grouped-query case; `attention_extra_plain`
+// gives the values that leave it as it was.
+struct AttentionExtra {
+  const void* q2;            // second source of query columns (null: none)
+  long long q2_stride;       // its row stride
+  int q2_head_stride;        // distance between two heads in q2
+  int q_split;               // query columns from here on come from q2
+  int q_head_stride;         // distance between two (virtual) heads in qkv
+  int k_row;                 // elements in a key row of the cache (>= maps * dim)
+  int v_row;                 // elements in a value row of the cache (>= vdim)
+  int v_in_k;                // values are the first vdim columns of the key rows
+  int chunk;                 // > 0: the chunk mask (window must be 0)
+  float lambda, out_scale, eps;   // the combination of two maps
+  int gate_elem_off;         // column of the element-wise gate in qkv (-1: none)
+  int no_trigger;            // the kernel after this one may be a library's: it starts only
+                             // when this one has completed
+};
+
 namespace {
+
+inline AttentionExtra attention_extra_plain(int dim, int vdim) {
+  AttentionExtra x = {};
+  x.q2 = nullptr;
+  x.q_split = dim;
+  x.q_head_stride = dim;
+  x.k_row = dim;
+  x.v_row = vdim;
+  x.gate_elem_off = -1;
+  x.out_scale = 1.f;
+  return x;
+}
+
+__device__ __forceinline__ int first_visible(int pos, int window, int chunk) {
+  if (chunk > 0) return pos - pos % chunk;
+  return (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+}
 
 template <typename T>
 __global__ void kv_store_kernel(const T* __restrict__ qkv, long long stride, int k_off, int v_off,
@@ -150,7 +197,7 @@ __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, flo
   }
 }
 
-template <int P, int VPL, typename T>
+template <int P, int VPL, int MAPS, typename T>
 __global__ void __launch_bounds__(512)
 distance_attention_tiled_kernel(
     const T* __restrict__ qkv, long long stride, int gate_off, T* __restrict__ out,
@@ -158,9 +205,11 @@ distance_attention_tiled_kernel(
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_seq,
     const int32_t* __restrict__ block_table, int max_blocks, int tokens, int heads, int kv_heads,
     int dim, int vdim, float scale, int window, const float* __restrict__ slope,
-    const float* __restrict__ rate, int splits, int row_floats, int stage_ok) {
+    const float* __restrict__ rate, int splits, int row_floats, int stage_ok,
+    const AttentionExtra x) {
+  static_assert(MAPS == 1 || P % MAPS == 0, "a head's maps stay in one warp");
   extern __shared__ __align__(16) float shared[];
-  let_next_kernel_start();
+  if (!x.no_trigger) let_next_kernel_start();
   wait_for_previous_kernel();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const int hg = heads / kv_heads, per_group = (hg + P - 1) / P;
@@ -179,8 +228,10 @@ distance_attention_tiled_kernel(
 #pragma unroll
     for (int i = 0; i < VPL; ++i) acc[p][i] = 0.f;
   }
-  const bool wide_k = dim % 8 == 0 && !((uintptr_t)k_cache & 15);
-  const bool wide_v = vdim % VPL == 0 && lane * VPL + VPL <= vdim && !((uintptr_t)v_cache & 15);
+  const int k_row = x.k_row, v_row = x.v_row;
+  const bool wide_k = dim % 8 == 0 && k_row % 8 == 0 && !((uintptr_t)k_cache & 15);
+  const bool wide_v = vdim % VPL == 0 && v_row % VPL == 0 && (v_row * sizeof(T)) % 16 == 0 &&
+                      lane * VPL + VPL <= vdim && !((uintptr_t)v_cache & 15);
   // (the same for every thread of the block)
   bool staged = false;
   int block_first = 0, block_last = 0;
@@ -191,7 +242,7 @@ distance_attention_tiled_kernel(
       if (token_seq[t0] == token_seq[t1] && positions[t1] == positions[t0] + warps - 1) {
         staged = true;
         const int p0 = positions[t0];
-        block_first = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
+        block_first = first_visible(p0, window, x.chunk);
         block_last = positions[t1];
       }
     }
@@ -204,16 +255,20 @@ distance_attention_tiled_kernel(
     h0 = g * hg + qi * P;
     np = hg - qi * P < P ? hg - qi * P : P;
     pos = positions[t];
-    first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    first = first_visible(pos, window, x.chunk);
+    const T* q2 = static_cast<const T*>(x.q2);
 #pragma unroll
     for (int p = 0; p < P; ++p) {
       if (p < np && slope) {
         sl[p] = slope[h0 + p];
         rt[p] = rate[h0 + p];
       }
+      const T* qa = qkv + (long long)t * stride + (long long)(h0 + p) * x.q_head_stride;
+      const T* qb = q2 ? q2 + (long long)t * x.q2_stride +
+                             (long long)(h0 + p) * x.q2_head_stride - x.q_split
+                       : qa;
       for (int e = lane; e < dim; e += 32)
-        mine[p * row_floats + e] =
-            p < np ? widen(qkv[(long long)t * stride + (long long)(h0 + p) * dim + e]) : 0.f;
+        mine[p * row_floats + e] = p < np ? widen(e < x.q_split ? qa[e] : qb[e]) : 0.f;
     }
     __syncwarp();
     const int32_t* table = block_table + (long long)token_seq[t] * max_blocks;
@@ -226,6 +281,8 @@ distance_attention_tiled_kernel(
 #pragma unroll
       for (int p = 0; p < P; ++p) s[p] = 0.f;
       if (valid) {
+#pragma unroll
+       for (int mm = 0; mm < MAPS; ++mm, kp += dim) {        // a map's key in the key row
         if (wide_k) {
           // four 16-byte pieces of the key's row are asked for before any is used
           for (int e = 0; e < dim; e += 32) {
@@ -237,7 +294,7 @@ distance_attention_tiled_kernel(
             for (int i = 0; i < 4; ++i) {
               if (e + 8 * i < dim) {
 #pragma unroll
-                for (int p = 0; p < P; ++p) {
+                for (int p = mm; p < P; p += MAPS) {
                   const float* q = mine + p * row_floats + e + 8 * i;
                   const float4 a = *reinterpret_cast<const float4*>(q);
                   const float4 b = *reinterpret_cast<const float4*>(q + 4);
@@ -253,9 +310,10 @@ distance_attention_tiled_kernel(
           for (int e = 0; e < dim; ++e) {
             const float kv = widen(kp[e]);
 #pragma unroll
-            for (int p = 0; p < P; ++p) s[p] = fmaf(mine[p * row_floats + e], kv, s[p]);
+            for (int p = mm; p < P; p += MAPS) s[p] = fmaf(mine[p * row_floats + e], kv, s[p]);
           }
         }
+       }
       }
       const float dist = (float)(pos - j);
       float w[P];
@@ -284,7 +342,11 @@ distance_attention_tiled_kernel(
           if (k0 + n > hi) continue;
           if (wide_v) {                    // a lane's columns in one access
             constexpr int kBytes = VPL * (int)sizeof(T);
-            if constexpr (kBytes == 32) {
+            if constexpr (kBytes == 64) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                reinterpret_cast<uint4*>(got[n])[q] = reinterpret_cast<const uint4*>(vr)[q];
+            } else if constexpr (kBytes == 32) {
               reinterpret_cast<uint4*>(got[n])[0] = reinterpret_cast<const uint4*>(vr)[0];
               reinterpret_cast<uint4*>(got[n])[1] = reinterpret_cast<const uint4*>(vr)[1];
             } else if constexpr (kBytes == 16) {
@@ -324,29 +386,29 @@ distance_attention_tiled_kernel(
     if (!staged) {
       for (int c = first / 32 + split; c <= pos / 32; c += splits) {
         const long long rows = rows_of(c);
-        chunk(c, k_cache + (rows + lane) * dim, v_cache + rows * vdim + lane * VPL, vdim);
+        chunk(c, k_cache + (rows + lane) * k_row, v_cache + rows * v_row + lane * VPL, v_row);
       }
     } else {
       // The block's four tokens follow one another in one sequence and see nearly the same
       // keys: every chunk is copied into shared memory once, a chunk ahead of its use, and
       // each warp scores the chunks of its own token's range from there.
       constexpr int kPiece = 16 / (int)sizeof(T);
-      const int kstride = dim + kPiece;              // padded: the lanes' rows hit different banks
+      const int kstride = k_row + kPiece;            // padded: the lanes' rows hit different banks
       T* stage = reinterpret_cast<T*>(shared + (long long)warps * P * row_floats);
-      const int per_buffer = 32 * (kstride + vdim);
+      const int per_buffer = 32 * (kstride + (x.v_in_k ? 0 : vdim));
       const int c_lo = block_first / 32, c_hi = block_last / 32;
       auto fetch = [&](int c, int buffer) {
         const long long rows = rows_of(c);
         T* ks = stage + buffer * per_buffer;
         T* vs = ks + 32 * kstride;
-        const int kp16 = dim / kPiece, vp16 = vdim / kPiece;
+        const int kp16 = k_row / kPiece, vp16 = x.v_in_k ? 0 : vdim / kPiece;
         for (int i = threadIdx.x; i < 32 * kp16; i += blockDim.x) {
           const int r = i / kp16, q = (i - r * kp16) * kPiece;
-          copy16_async(ks + r * kstride + q, k_cache + (rows + r) * dim + q);
+          copy16_async(ks + r * kstride + q, k_cache + (rows + r) * k_row + q);
         }
         for (int i = threadIdx.x; i < 32 * vp16; i += blockDim.x) {
           const int r = i / vp16, q = (i - r * vp16) * kPiece;
-          copy16_async(vs + r * vdim + q, v_cache + (rows + r) * vdim + q);
+          copy16_async(vs + r * vdim + q, v_cache + (rows + r) * v_row + q);
         }
         copies_commit();
       };
@@ -359,7 +421,8 @@ distance_attention_tiled_kernel(
         __syncthreads();
         if (c >= first / 32 && c <= pos / 32) {
           const T* ks = stage + buffer * per_buffer;
-          chunk(c, ks + lane * kstride, ks + 32 * kstride + lane * VPL, vdim);
+          if (x.v_in_k) chunk(c, ks + lane * kstride, ks + lane * VPL, kstride);
+          else chunk(c, ks + lane * kstride, ks + 32 * kstride + lane * VPL, vdim);
         }
         __syncthreads();
       }
@@ -404,6 +467,36 @@ distance_attention_tiled_kernel(
     }
   }
   if (!active) return;
+  if constexpr (MAPS == 2) {
+    // two maps a head over the same values: o = a1 - lambda a2, unit root mean square over
+    // the head's values, the scale, and the gate element by element
+#pragma unroll
+    for (int p = 0; p < P; p += 2) {
+      if (p >= np) continue;
+      const float i1 = 1.f / l[p], i2 = x.lambda / l[p + 1];
+      float o[VPL], ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        o[i] = lane * VPL + i < vdim ? acc[p][i] * i1 - acc[p + 1][i] * i2 : 0.f;
+        ss = fmaf(o[i], o[i], ss);
+      }
+      const float r = rsqrtf(warp_sum(ss) / (float)vdim + x.eps) * x.out_scale;
+      const long long head = (long long)t * (heads / 2) + (h0 + p) / 2;
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const int col = lane * VPL + i;
+        if (col >= vdim) continue;
+        float gate = 1.f;
+        if (x.gate_elem_off >= 0) {
+          const float z = widen(qkv[(long long)t * stride + x.gate_elem_off +
+                                    (long long)((h0 + p) / 2) * vdim + col]);
+          gate = 1.f / (1.f + expf(-z));
+        }
+        out[head * vdim + col] = narrow<T>(o[i] * r * gate);
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int p = 0; p < P; ++p) {
     if (p >= np) continue;
@@ -420,15 +513,15 @@ distance_attention_tiled_kernel(
   }
 }
 
-template <int P, int VPL, typename T>
+template <int P, int VPL, int MAPS, typename T>
 int launch_tiled(const void* qkv, long long stride, int gate_off, void* out, const void* k_cache,
                  const void* v_cache, const int32_t* positions, const int32_t* token_seq,
                  const int32_t* block_table, int max_blocks, int tokens, int heads, int kv_heads,
                  int dim, int vdim, float scale, int window, const float* slope,
-                 const float* rate, int splits, cudaStream_t stream) {
-  constexpr int kBudget = 96 * 1024;
+                 const float* rate, int splits, const AttentionExtra& x, cudaStream_t stream) {
+  constexpr int kBudget = 200 * 1024;
   static PerDeviceOnce configured;
-  auto kernel = distance_attention_tiled_kernel<P, VPL, T>;
+  auto kernel = distance_attention_tiled_kernel<P, VPL, MAPS, T>;
   if (configured.needs()) {
     const cudaError_t e =
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBudget);
@@ -444,9 +537,11 @@ int launch_tiled(const void* qkv, long long stride, int gate_off, void* out, con
   if (splits > 1) splits = warps;
   // prompts: room for two chunks of keys and values that a block's tokens share
   size_t smem = (size_t)warps * P * row_floats * sizeof(float);
-  const size_t staging = (size_t)2 * 32 * (dim + 16 / sizeof(T) + vdim) * sizeof(T);
+  const size_t staging =
+      (size_t)2 * 32 * (x.k_row + 16 / sizeof(T) + (x.v_in_k ? 0 : vdim)) * sizeof(T);
   const int stage_ok = splits == 1 && warps >= 4 && tokens >= warps &&
-                       (dim * sizeof(T)) % 16 == 0 && (vdim * sizeof(T)) % 16 == 0 &&
+                       (x.k_row * sizeof(T)) % 16 == 0 && (vdim * sizeof(T)) % 16 == 0 &&
+                       (x.v_row * sizeof(T)) % 16 == 0 &&
                        !((uintptr_t)k_cache & 15) && !((uintptr_t)v_cache & 15) &&
                        smem + staging <= (size_t)kBudget;
   if (stage_ok) smem += staging;
@@ -457,7 +552,7 @@ int launch_tiled(const void* qkv, long long stride, int gate_off, void* out, con
                            (const T*)qkv, stride, gate_off, (T*)out, (const T*)k_cache,
                            (const T*)v_cache, positions, token_seq, block_table, max_blocks,
                            tokens, heads, kv_heads, dim, vdim, scale, window, slope, rate, splits,
-                           row_floats, stage_ok);
+                           row_floats, stage_ok, x);
 }
 
 template <typename T>
@@ -465,20 +560,29 @@ int pick_tiled(const void* qkv, long long stride, int gate_off, void* out, const
                const void* v_cache, const int32_t* positions, const int32_t* token_seq,
                const int32_t* block_table, int max_blocks, int tokens, int heads, int kv_heads,
                int dim, int vdim, float scale, int window, const float* slope, const float* rate,
-               int splits, cudaStream_t stream) {
-  const int hg = heads / kv_heads;
-#define SAKV_TILED(P, VPL)                                                                       \
-  return launch_tiled<P, VPL, T>(qkv, stride, gate_off, out, k_cache, v_cache, positions,        \
-                                 token_seq, block_table, max_blocks, tokens, heads, kv_heads, dim, \
-                                 vdim, scale, window, slope, rate, splits, stream)
-#define SAKV_TILED_P(VPL)          \
-  if (hg == 1) SAKV_TILED(1, VPL); \
-  if (hg == 2) SAKV_TILED(2, VPL); \
-  SAKV_TILED(4, VPL)
+               int splits, int maps, const AttentionExtra& x, cudaStream_t stream) {
+  const int hg = heads / kv_heads;       // (virtual heads: a head's maps count one each)
+#define SAKV_TILED(P, VPL, MAPS)                                                                 \
+  return launch_tiled<P, VPL, MAPS, T>(qkv, stride, gate_off, out, k_cache, v_cache, positions,  \
+                                       token_seq, block_table, max_blocks, tokens, heads,        \
+                                       kv_heads, dim, vdim, scale, window, slope, rate, splits,  \
+                                       x, stream)
+#define SAKV_TILED_P(VPL)                        \
+  if (maps == 2) {                               \
+    if (hg == 2) SAKV_TILED(2, VPL, 2);          \
+    SAKV_TILED(4, VPL, 2);                       \
+  }                                              \
+  if (hg == 1) SAKV_TILED(1, VPL, 1);            \
+  if (hg == 2) SAKV_TILED(2, VPL, 1);            \
+  SAKV_TILED(4, VPL, 1)
   if (vdim <= 32) { SAKV_TILED_P(1); }
   if (vdim <= 64) { SAKV_TILED_P(2); }
   if (vdim <= 128) { SAKV_TILED_P(4); }
-  SAKV_TILED_P(8);
+  if (vdim <= 256) { SAKV_TILED_P(8); }
+  // (sixteen columns a lane: two heads a warp at most, for the registers' sake)
+  if (maps == 2) SAKV_TILED(2, 16, 2);
+  if (hg == 1) SAKV_TILED(1, 16, 1);
+  SAKV_TILED(2, 16, 1);
 #undef SAKV_TILED_P
 #undef SAKV_TILED
 }
@@ -549,14 +653,15 @@ SAKV_EXPORT int sakv_distance_attention(const void* qkv, int dtype, long long st
     return cudaErrorInvalidValue;
   if (tokens == 0) return 0;
   if (splits > 0 && dim <= 256 && vdim <= 256) {
+    const AttentionExtra x = attention_extra_plain(dim, vdim);
     if (dtype == SAKV_F32)
       return pick_tiled<float>(qkv, stride, gate_off, out, k_cache, v_cache, positions, token_seq,
                                block_table, max_blocks, tokens, heads, kv_heads, dim, vdim, scale,
-                               window, slope, rate, splits, stream);
+                               window, slope, rate, splits, 1, x, stream);
     if (dtype == SAKV_BF16)
       return pick_tiled<__nv_bfloat16>(qkv, stride, gate_off, out, k_cache, v_cache, positions,
                                        token_seq, block_table, max_blocks, tokens, heads, kv_heads,
-                                       dim, vdim, scale, window, slope, rate, splits, stream);
+                                       dim, vdim, scale, window, slope, rate, splits, 1, x, stream);
     return cudaErrorInvalidValue;
   }
   if (dtype == SAKV_F32)
@@ -568,5 +673,58 @@ SAKV_EXPORT int sakv_distance_attention(const void* qkv, int dtype, long long st
                                            positions, token_seq, block_table, max_blocks, tokens,
                                            heads, kv_heads, dim, vdim, scale, window, slope, rate,
                                            stream);
+  return cudaErrorInvalidValue;
+}
+
+// The tiled form with everything `AttentionExtra` describes. `heads` counts query heads;
+// each has `maps` (1 or 2) queries of `dim` columns, `q_head_stride` apart in qkv. Query
+// columns from `q_split` on are read from `q2` (null: all from qkv). Keys: rows of `k_row`
+// elements, map m's key at column m * dim; values: the first `vdim` of rows of `v_row`
+// elements in v_cache, or (v_cache null) of the key rows. `chunk` > 0 is the chunk mask;
+// `window` and `chunk` exclude each other. With two maps: lambda, out_scale, eps and
+// gate_elem_off (the element-wise gate's first column in qkv, -1 for none) shape the output;
+// with one map `gate_off` is the gate a head as above. out: [tokens, heads * vdim].
+// `splits` >= 1 as above.
+SAKV_EXPORT int sakv_cached_attention(
+    const void* qkv, int dtype, long long stride, int q_head_stride, const void* q2,
+    long long q2_stride, int q2_head_stride, int q_split, int gate_off, void* out,
+    const void* k_cache, int k_row, const void* v_cache, int v_row,
+    const int32_t* positions, const int32_t* token_seq, const int32_t* block_table,
+    int max_blocks, int tokens, int heads, int kv_heads, int maps, int dim, int vdim, float scale,
+    int window, int chunk, float lambda, float out_scale, float eps, int gate_elem_off,
+    int splits, cudaStream_t stream) {
+  if (tokens < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || vdim <= 0 ||
+      dim > 640 || vdim > 512 || max_blocks <= 0 || window < 0 || chunk < 0 ||
+      (window > 0 && chunk > 0) || splits < 1 || splits > 16 || (maps != 1 && maps != 2) ||
+      k_row < maps * dim || (q2 != nullptr && (q_split < 0 || q_split > dim)) ||
+      q_head_stride <= 0)
+    return cudaErrorInvalidValue;
+  if (tokens == 0) return 0;
+  AttentionExtra x = {};
+  x.q2 = q2;
+  x.q2_stride = q2_stride;
+  x.q2_head_stride = q2_head_stride;
+  x.q_split = q2 ? q_split : dim;
+  x.q_head_stride = q_head_stride;
+  x.k_row = k_row;
+  x.v_in_k = v_cache == nullptr;
+  x.v_row = x.v_in_k ? k_row : v_row;
+  if (x.v_row < vdim) return cudaErrorInvalidValue;
+  x.chunk = chunk;
+  x.lambda = lambda;
+  x.out_scale = out_scale;
+  x.eps = eps;
+  x.gate_elem_off = gate_elem_off;
+  x.no_trigger = 1;
+  const void* values = x.v_in_k ? k_cache : v_cache;
+  if (dtype == SAKV_F32)
+    return pick_tiled<float>(qkv, stride, gate_off, out, k_cache, values, positions, token_seq,
+                             block_table, max_blocks, tokens, heads * maps, kv_heads, dim, vdim,
+                             scale, window, nullptr, nullptr, splits, maps, x, stream);
+  if (dtype == SAKV_BF16)
+    return pick_tiled<__nv_bfloat16>(qkv, stride, gate_off, out, k_cache, values, positions,
+                                     token_seq, block_table, max_blocks, tokens, heads * maps,
+                                     kv_heads, dim, vdim, scale, window, nullptr, nullptr, splits,
+                                     maps, x, stream);
   return cudaErrorInvalidValue;
 }

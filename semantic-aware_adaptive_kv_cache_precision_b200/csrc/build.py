@@ -50,6 +50,9 @@ LIBRARIES = {
     "streams": "streams.cu",
     "delta_rule": "delta_rule.cu",
     "attention_distance": "attention_distance.cu",
+    "layer_norm": "layer_norm.cu",
+    "latent": "latent.cu",
+    "moe": "moe.cu",
 }
 
 #: extra flags of single libraries (libraries that need the driver API, for instance)

@@ -11,6 +11,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define SAKV_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -84,9 +85,17 @@ static inline int launch_overlapped_cluster(void (*kernel)(KernelArgs...), dim3 
   config.stream = stream;
   cudaLaunchAttribute attr[3];
   int n = 0;
-  attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[n].val.programmaticStreamSerializationAllowed = 1;
-  ++n;
+  // SAKV_NO_OVERLAP=1 in the environment launches every kernel after the one before it has
+  // completed (for telling an ordering fault from any other)
+  static const bool overlap = []() {
+    const char* v = getenv("SAKV_NO_OVERLAP");
+    return !(v && v[0] == '1');
+  }();
+  if (overlap) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
   if (cluster.x * cluster.y * cluster.z > 1) {
     attr[n].id = cudaLaunchAttributeClusterDimension;
     attr[n].val.clusterDim.x = cluster.x;
@@ -111,6 +120,22 @@ static inline int launch_overlapped(void (*kernel)(KernelArgs...), dim3 grid, di
   return launch_overlapped_cluster(kernel, grid, block, smem, stream,
                                    dim3(1, 1, cluster_z > 1 ? cluster_z : 1),
                                    static_cast<Args&&>(args)...);
+}
+
+// A launch in plain stream order: the kernel begins after everything before it on the stream
+// has completed, and (unless it asks for it itself) nothing after it begins before it has.
+// For kernels that sit between library calls or whose inputs are indices made by the
+// kernels just before them.
+template <typename... KernelArgs, typename... Args>
+static inline int launch_ordered(void (*kernel)(KernelArgs...), dim3 grid, dim3 block,
+                                 size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  const cudaError_t e = cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+  return e != cudaSuccess ? static_cast<int>(e) : launch_status();
 }
 
 // The number of SMs of the current device, asked once per device (148 on a B200; fewer on

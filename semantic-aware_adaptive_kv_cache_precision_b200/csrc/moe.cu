@@ -1,0 +1,312 @@
+// A mixture of small gated feed-forwards, routed on the device.
+//
+//   route    a warp a token: the `top` largest router logits (ties: the lowest index), their
+//            sigmoids as weights, and the token's place among the rows of each chosen expert
+//   plan     one block: where each expert's rows begin and which (expert, first row) every
+//            tile of `TM` rows of the grouped products covers
+//   gather   the experts' input rows, sorted by expert: x * weight (the weight multiplies an
+//            expert's INPUT) rounded once to the activations' type
+//   products out = rows x W[e]^T for every tile, with the weights of the tile's expert:
+//            the gated pair with the clamped activation in its epilogue
+//              g = min(., limit), u = clamp(., -limit, limit), y = g * sigmoid(alpha g) * (u + 1)
+//            and the plain product that leaves fp32
+//   combine  a token's rows summed in the order of its choices, plus the shared expert's
+//            output times sigmoid of its gate's logit
+//
+// Nothing is read back by the host: the grid of the products is sized for the most tiles
+// there can be, and blocks beyond the planned count leave at once. A row's result does not
+// depend on which other rows share its tile (every output adds its products for k = 0, 1,
+// 2, ... in that order), so the unordered placement of rows inside an expert changes nothing.
+#include "common.cuh"
+#include "mma.cuh"
+
+namespace {
+
+constexpr int TM = 32;          // rows of a tile
+constexpr int TN = 64;          // output columns of a tile
+constexpr int TK = 32;          // K step
+
+__global__ void route_kernel(const float* __restrict__ logits, long long ld, int experts, int top,
+                             int32_t* __restrict__ chosen, float* __restrict__ weights,
+                             int32_t* __restrict__ counts, int32_t* __restrict__ rank,
+                             int tokens) {
+  const long long t = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (t >= tokens) return;
+  const float* z = logits + t * ld;
+  uint32_t taken = 0;                              // bit i: this lane's i-th expert is chosen
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int i = 0, e = lane; e < experts; ++i, e += 32) {
+      if (taken >> i & 1) continue;
+      const float v = z[e];
+      if (v > best || (at == 0x7fffffff && !(v != v))) {
+        best = v;
+        at = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) {
+        best = ob;
+        at = oa;
+      }
+    }
+    if (at == 0x7fffffff) at = k;                  // (a row without a finite logit)
+    if ((at & 31) == lane) taken |= 1u << (at >> 5);
+    if (lane == 0) {
+      chosen[t * top + k] = at;
+      weights[t * top + k] = 1.f / (1.f + expf(-best));
+      rank[t * top + k] = atomicAdd(counts + at, 1);
+    }
+  }
+}
+
+__global__ void plan_kernel(int32_t* __restrict__ counts, int32_t* __restrict__ offsets,
+                            int32_t* __restrict__ tile_expert, int32_t* __restrict__ tile_row,
+                            int32_t* __restrict__ n_tiles, int experts, int max_tiles) {
+  extern __shared__ int32_t base[];                // [experts + 1] first tile of each expert
+  if (threadIdx.x == 0) {
+    int rows = 0, tiles = 0;
+    for (int e = 0; e < experts; ++e) {
+      offsets[e] = rows;
+      base[e] = tiles;
+      rows += counts[e];
+      tiles += (counts[e] + TM - 1) / TM;
+    }
+    offsets[experts] = rows;
+    base[experts] = tiles;
+    *n_tiles = tiles < max_tiles ? tiles : max_tiles;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    const int n = base[e + 1] - base[e];
+    for (int i = 0; i < n; ++i) {
+      if (base[e] + i >= max_tiles) break;
+      tile_expert[base[e] + i] = e;
+      tile_row[base[e] + i] = offsets[e] + i * TM;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;     // for the next step
+}
+
+template <typename T>
+__global__ void gather_kernel(const T* __restrict__ h, const int32_t* __restrict__ chosen,
+                              const float* __restrict__ weights, const int32_t* __restrict__ rank,
+                              const int32_t* __restrict__ offsets, T* __restrict__ rows,
+                              int32_t* __restrict__ slot_of, int top, int width,
+                              int weight_input) {
+  const long long pair = blockIdx.x;                // token * top + k
+  const long long t = pair / top;
+  const int slot = offsets[chosen[pair]] + rank[pair];
+  const float w = weight_input ? weights[pair] : 1.f;
+  if (threadIdx.x == 0) slot_of[pair] = slot;
+  const T* from = h + t * width;
+  T* to = rows + (long long)slot * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) to[i] = narrow<T>(widen(from[i]) * w);
+}
+
+// One tile of a grouped product: rows [row0, row0 + TM) of `a` (those below `row_end`) times
+// the expert's weights. DUAL: two weight matrices (gate and up) and the activation; else one
+// and fp32 out. 256 threads; a thread owns 2 rows x 4 columns.
+template <typename T, bool DUAL>
+__global__ void __launch_bounds__(256)
+grouped_kernel(const T* __restrict__ a, const T* __restrict__ w0, const T* __restrict__ w1,
+               long long expert_stride, const int32_t* __restrict__ tile_expert,
+               const int32_t* __restrict__ tile_row, const int32_t* __restrict__ offsets,
+               const int32_t* __restrict__ n_tiles, void* __restrict__ out_v, int n, int k,
+               float limit, float alpha) {
+  __shared__ float as[TK][TM + 4];
+  __shared__ float ws[DUAL ? 2 : 1][TK][TN + 4];
+  if ((int)blockIdx.x >= *n_tiles) return;
+  const int e = tile_expert[blockIdx.x], row0 = tile_row[blockIdx.x];
+  const int row_end = offsets[e + 1];
+  const int n0 = blockIdx.y * TN;
+  const T* wa = w0 + (long long)e * expert_stride;
+  const T* wb = DUAL ? w1 + (long long)e * expert_stride : nullptr;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[DUAL ? 2 : 1][2][4] = {};
+  for (int k0 = 0; k0 < k; k0 += TK) {
+    for (int i = threadIdx.x; i < TM * TK; i += 256) {
+      const int r = i / TK, c = i % TK;
+      as[c][r] = (row0 + r < row_end && k0 + c < k)
+                     ? widen(a[(long long)(row0 + r) * k + k0 + c]) : 0.f;
+    }
+    for (int i = threadIdx.x; i < TN * TK; i += 256) {
+      const int r = i / TK, c = i % TK;
+      const bool ok = n0 + r < n && k0 + c < k;
+      ws[0][c][r] = ok ? widen(wa[(long long)(n0 + r) * k + k0 + c]) : 0.f;
+      if (DUAL) ws[1][c][r] = ok ? widen(wb[(long long)(n0 + r) * k + k0 + c]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < TK; ++c) {
+      const float a0 = as[c][ty * 2], a1 = as[c][ty * 2 + 1];
+#pragma unroll
+      for (int m = 0; m < (DUAL ? 2 : 1); ++m) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float w = ws[m][c][tx * 4 + j];
+          acc[m][0][j] = fmaf(a0, w, acc[m][0][j]);
+          acc[m][1][j] = fmaf(a1, w, acc[m][1][j]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int row = row0 + ty * 2 + i;
+    if (row >= row_end) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int col = n0 + tx * 4 + j;
+      if (col >= n) continue;
+      if constexpr (DUAL) {
+        const float g = fminf(acc[0][i][j], limit);
+        const float u = fminf(fmaxf(acc[1][i][j], -limit), limit);
+        const float y = g / (1.f + expf(-alpha * g)) * (u + 1.f);
+        static_cast<T*>(out_v)[(long long)row * n + col] = narrow<T>(y);
+      } else {
+        static_cast<float*>(out_v)[(long long)row * n + col] = acc[0][i][j];
+      }
+    }
+  }
+}
+
+// The dense form of the same activation for the shared expert: gate_up [T, 2 ff] -> [T, ff].
+template <typename T>
+__global__ void clamped_act_kernel(const T* __restrict__ gate_up, T* __restrict__ out,
+                                   long long count, int ff, float limit, float alpha) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / ff;
+    const int c = static_cast<int>(i - t * ff);
+    const float g = fminf(widen(gate_up[t * 2 * ff + c]), limit);
+    const float u = fminf(fmaxf(widen(gate_up[t * 2 * ff + ff + c]), -limit), limit);
+    out[i] = narrow<T>(g / (1.f + expf(-alpha * g)) * (u + 1.f));
+  }
+}
+
+__global__ void combine_kernel(const float* __restrict__ rows, const int32_t* __restrict__ slot_of,
+                               const float* __restrict__ weights, int weight_output,
+                               const float* __restrict__ shared, const float* __restrict__ gate,
+                               long long gate_ld, float* __restrict__ out, int top, int width,
+                               long long count) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / width;
+    const int c = static_cast<int>(i - t * width);
+    float sum = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const float v = rows[(long long)slot_of[t * top + k] * width + c];
+      sum += weight_output ? v * weights[t * top + k] : v;
+    }
+    if (shared) {
+      const float s = gate ? 1.f / (1.f + expf(-gate[t * gate_ld])) : 1.f;
+      sum = fmaf(shared[i], s, sum);
+    }
+    out[i] = sum;
+  }
+}
+
+}  // namespace
+
+SAKV_EXPORT int sakv_moe_tile_rows() { return TM; }
+
+// logits: fp32 [tokens, ld] (the first `experts` columns); counts: int32 [experts], zero on
+// entry (plan leaves it zero again). chosen, rank: int32 [tokens, top]; weights: fp32.
+SAKV_EXPORT int sakv_moe_route(const float* logits, long long ld, int experts, int top,
+                               int32_t* chosen, float* weights, int32_t* counts, int32_t* rank,
+                               int tokens, cudaStream_t stream) {
+  if (tokens < 0 || experts <= 0 || experts > 1024 || top <= 0 || top > experts || top > 32 ||
+      ld < experts)
+    return cudaErrorInvalidValue;
+  if (tokens == 0) return 0;
+  const int threads = 128;
+  const long long blocks = ((long long)tokens * 32 + threads - 1) / threads;
+  return launch_ordered(route_kernel, dim3((unsigned)blocks), dim3(threads), 0, stream, logits, ld, experts, top, chosen, weights, counts, rank, tokens);
+}
+
+SAKV_EXPORT int sakv_moe_plan(int32_t* counts, int32_t* offsets, int32_t* tile_expert,
+                              int32_t* tile_row, int32_t* n_tiles, int experts, int max_tiles,
+                              cudaStream_t stream) {
+  if (experts <= 0 || experts > 1024 || max_tiles <= 0) return cudaErrorInvalidValue;
+  return launch_ordered(plan_kernel, dim3(1), dim3(256), (size_t)(experts + 1) * 4, stream, counts, offsets, tile_expert, tile_row, n_tiles, experts, max_tiles);
+}
+
+SAKV_EXPORT int sakv_moe_gather(const void* h, int dtype, const int32_t* chosen,
+                                const float* weights, const int32_t* rank, const int32_t* offsets,
+                                void* rows, int32_t* slot_of, int tokens, int top, int width,
+                                int weight_input, cudaStream_t stream) {
+  if (tokens < 0 || top <= 0 || width <= 0) return cudaErrorInvalidValue;
+  if (tokens == 0) return 0;
+  const dim3 grid((unsigned)((long long)tokens * top)), block(width >= 1024 ? 256 : 128);
+  if (dtype == SAKV_F32)
+    return launch_ordered(gather_kernel<float>, grid, block, 0, stream, (const float*)h,
+                             chosen, weights, rank, offsets, (float*)rows, slot_of, top, width,
+                             weight_input);
+  if (dtype == SAKV_BF16)
+    return launch_ordered(gather_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)h, chosen, weights, rank, offsets,
+                             (__nv_bfloat16*)rows, slot_of, top, width, weight_input);
+  return cudaErrorInvalidValue;
+}
+
+// a: [rows, k] of `dtype`, sorted by expert. w0 (and w1 when `dual`): the experts' weights,
+// expert e's [n, k] at w + e * expert_stride. dual: out [rows, n] of `dtype` = the clamped
+// gated activation of (a w0^T, a w1^T); else out fp32 [rows, n] = a w0^T.
+SAKV_EXPORT int sakv_moe_product(const void* a, int dtype, const void* w0, const void* w1,
+                                 long long expert_stride, const int32_t* tile_expert,
+                                 const int32_t* tile_row, const int32_t* offsets,
+                                 const int32_t* n_tiles, int max_tiles, void* out, int n, int k,
+                                 int dual, float limit, float alpha, cudaStream_t stream) {
+  if (max_tiles <= 0 || n <= 0 || k <= 0 || (dual && !w1)) return cudaErrorInvalidValue;
+  const dim3 grid(max_tiles, (n + TN - 1) / TN), block(256);
+  if (grid.y > 65535) return cudaErrorInvalidValue;
+#define SAKV_GROUPED(T, DUAL)                                                                    \
+  return launch_ordered(grouped_kernel<T, DUAL>, grid, block, 0, stream, (const T*)a,      \
+                           (const T*)w0, (const T*)w1, expert_stride, tile_expert, tile_row,     \
+                           offsets, n_tiles, out, n, k, limit, alpha)
+  if (dtype == SAKV_F32) {
+    if (dual) SAKV_GROUPED(float, true);
+    SAKV_GROUPED(float, false);
+  }
+  if (dtype == SAKV_BF16) {
+    if (dual) SAKV_GROUPED(__nv_bfloat16, true);
+    SAKV_GROUPED(__nv_bfloat16, false);
+  }
+#undef SAKV_GROUPED
+  return cudaErrorInvalidValue;
+}
+
+SAKV_EXPORT int sakv_clamped_act(const void* gate_up, void* out, int dtype, int tokens, int ff,
+                                 float limit, float alpha, cudaStream_t stream) {
+  if (tokens < 0 || ff <= 0) return cudaErrorInvalidValue;
+  if (tokens == 0) return 0;
+  const long long count = (long long)tokens * ff;
+  const dim3 grid(grid_for(count, 256)), block(256);
+  if (dtype == SAKV_F32)
+    return launch_ordered(clamped_act_kernel<float>, grid, block, 0, stream, (const float*)gate_up, (float*)out, count, ff, limit, alpha);
+  if (dtype == SAKV_BF16)
+    return launch_ordered(clamped_act_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, count, ff, limit,
+                             alpha);
+  return cudaErrorInvalidValue;
+}
+
+// out[t] = sum_k rows[slot_of[t, k]] (* weights[t, k] if weight_output) + shared[t] *
+// sigmoid(gate[t * gate_ld]); shared and gate may be null.
+SAKV_EXPORT int sakv_moe_combine(const float* rows, const int32_t* slot_of, const float* weights,
+                                 int weight_output, const float* shared, const float* gate,
+                                 long long gate_ld, float* out, int tokens, int top, int width,
+                                 cudaStream_t stream) {
+  if (tokens < 0 || top <= 0 || width <= 0) return cudaErrorInvalidValue;
+  if (tokens == 0) return 0;
+  const long long count = (long long)tokens * width;
+  return launch_ordered(combine_kernel, dim3(grid_for(count, 256)), dim3(256), 0, stream,
+                           rows, slot_of, weights, weight_output, shared, gate, gate_ld, out, top,
+                           width, count);
+}

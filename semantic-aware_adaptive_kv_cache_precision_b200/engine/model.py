@@ -42,6 +42,8 @@ class DecoderModel:
         for block in self.blocks:
             decls += block.tensor_decls()
         decls += self.final_norm.tensor_decls()
+        if spec.input_mix_name:
+            decls.append(TensorDecl(spec.input_mix_name, (spec.hidden, 2 * spec.hidden)))
         if not spec.tie_head:
             decls.append(TensorDecl(spec.head_name, (spec.vocab_size, spec.hidden)))
         if spec.head_bias_name:
@@ -65,6 +67,7 @@ class DecoderModel:
         self.embed = arena.view(self.spec.embed_name)
         self.head = self.embed if self.spec.tie_head else arena.view(self.spec.head_name)
         self.head_bias = arena.view(self.spec.head_bias_name) if self.spec.head_bias_name else None
+        self.input_mix = arena.view(self.spec.input_mix_name) if self.spec.input_mix_name else None
         for block in self.blocks:
             block.bind(arena)
         self.final_norm.bind(arena)
@@ -114,12 +117,27 @@ class DecoderModel:
 
         if capture is not None:
             capture.append(stream(x))
+        # calls with `mix_input` replace the stream by W [x; x0]: the two halves of the
+        # product's input lie side by side, the embedding's output in the second for good
+        both = None
+        if self.input_mix is not None and any(c.mix_input for c in self.spec.run_order):
+            if streams > 1:
+                raise ValueError("the input mix is not built for several streams")
+            both = torch.empty((step.tokens, 2 * self.spec.hidden), dtype=self.act_dtype,
+                               device=self.device)
+            both[:, self.spec.hidden:].copy_(x)
         written = set()
         pending = None          # a block's last output, not yet added to the stream
         last = len(self.spec.run_order) - 1
         for i, call in enumerate(self.spec.run_order):
             view = cache.entry_view(call.cache, step.tables)
             block = self.blocks[call.block]
+            if call.mix_input and both is not None:
+                if pending is not None:
+                    _settle(x, pending)
+                    pending = None
+                both[:, :self.spec.hidden].copy_(x)
+                x = ops.linear(both, self.input_mix, out_dtype=torch.float32)
             if getattr(block, "carries_pending", False):
                 pending = block.forward(x, step, view, call.cache not in written, pending,
                                         leave_pending=i < last and capture is None)

@@ -16,6 +16,8 @@ from .linear import Deferred, gated_up, linear
 from . import gemm_tc
 from .streams import streams_spread, streams_step, token_shift
 from .recurrent import delta_rule
+from . import mixture
+from .mixture import latent_prepare, rotate_heads
 from .attention import (attention_decode, attention_prefill, attention_prefill_tc, decode_splits,
                         forget_descriptors,
                         fast_path_takes, kernel_errors, plan_wide_tiles, tc_prefill_takes, upload_query_tiles,
@@ -26,7 +28,8 @@ __all__ = ["CACHE_BLOCK", "KernelError", "embed", "rms_norm", "rope_store", "att
            "upload_query_tiles",
            "decode_splits", "fast_path_takes", "forget_descriptors",
            "kernel_errors", "gated_silu", "gelu_tanh", "streams_step", "streams_spread", "token_shift",
-           "delta_rule", "kv_store", "distance_attention", "gated_up", "gemm_tc", "add_into", "scale_cap_", "linear", "choose", "Deferred"]
+           "delta_rule", "kv_store", "layer_norm", "cached_attention", "mixture", "latent_prepare",
+           "rotate_heads", "distance_attention", "gated_up", "gemm_tc", "add_into", "scale_cap_", "linear", "choose", "Deferred"]
 
 
 def _check(cond: bool, message: str) -> None:
@@ -208,6 +211,92 @@ def distance_attention(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
          -1 if gate_off is None else int(gate_off), ptr(out), ptr(k_cache), ptr(v_cache),
          ptr(positions), ptr(token_seq), ptr(block_table), block_table.shape[1], tokens, heads,
          kv_heads, dim, vdim, float(scale), int(window) if window else 0, ptr(slope), ptr(rate),
+         int(splits))
+    return out
+
+
+def layer_norm(x: torch.Tensor, weight: torch.Tensor | None, eps: float, out_dtype: torch.dtype,
+               rows: torch.Tensor | None = None, add: torch.Tensor | None = None,
+               add_weight: torch.Tensor | None = None) -> torch.Tensor | None:
+    """Layer norm (weight, no bias) of rows of fp32 `x`; with `rows` (int32), of those rows
+    only. With `add` (fp32, x's shape) and `add_weight`, `x += layer_norm(add) * add_weight`
+    happens first, in the same kernel, and x keeps the sum; `weight` None then returns nothing
+    (only the stream is completed)."""
+    require_cuda(x, weight, rows, add, add_weight)
+    _check(x.dtype == torch.float32 and x.dim() == 2 and x.is_contiguous(), "x: fp32 [T, hidden]")
+    hidden = x.shape[1]
+    for w in (weight, add_weight):
+        _check(w is None or (w.shape == (hidden,) and w.is_contiguous()), "weight: [hidden]")
+    _check(weight is not None or add is not None, "layer_norm: nothing to do")
+    _check((add is None) == (add_weight is None), "add and add_weight come together")
+    if add is not None:
+        _check(rows is None and add.dtype == torch.float32 and add.is_contiguous()
+               and add.shape == x.shape, "add: fp32 like x, no rows")
+        _check(weight is None or weight.dtype == add_weight.dtype, "the weights' types differ")
+    n = x.shape[0]
+    if rows is not None:
+        _check(rows.dtype == torch.int32 and rows.dim() == 1 and rows.is_contiguous(),
+               "rows: int32 [R]")
+        n = rows.numel()
+    out = None if weight is None else torch.empty((n, hidden), dtype=out_dtype, device=x.device)
+    w_dtype = (weight if weight is not None else add_weight).dtype
+    call("sakv_layer_norm", ptr(x), ptr(add), ptr(add_weight), ptr(rows), ptr(weight),
+         dtype_code(w_dtype), ptr(out), dtype_code(out_dtype if out is not None else torch.float32),
+         n, hidden, float(eps))
+    return out
+
+
+def cached_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor | None,
+                     positions: torch.Tensor, token_seq: torch.Tensor, block_table: torch.Tensor,
+                     heads: int, dim: int, vdim: int, scale: float, *, maps: int = 1,
+                     q2: torch.Tensor | None = None, q_split: int = 0,
+                     window: int | None = None, chunk: int | None = None, lam: float = 0.0,
+                     out_scale: float = 1.0, eps: float = 0.0, gate_elem_off: int | None = None,
+                     splits: int = 1) -> torch.Tensor:
+    """Causal attention of every token of the step over its sequence's cache, in the general
+    form of `csrc/attention_distance.cu`: scores, softmax weights and weighted sums in fp32.
+
+    `q`: [T, heads * maps, width] with any strides between tokens and heads (a view of a
+    projection's output): head h's `maps` queries are its rows h * maps .. h * maps + maps - 1,
+    each `dim` columns. With `q2` ([T, heads * maps, dim - q_split], strided likewise) a query's
+    columns from `q_split` on come from q2. `k_cache`: [blocks, kv_heads, 64, k_row] with map
+    m's key at column m * dim; `v_cache`: [blocks, kv_heads, 64, v_row] of which the first
+    `vdim` are read, or None: the values are the first `vdim` columns of the key rows. `window`
+    (the last w keys) or `chunk` (keys of the query's own run of c positions) or neither. Two
+    maps are combined as `a1 - lam * a2`, divided by their root mean square over vdim (+ eps),
+    times `out_scale`, times the sigmoid of the `vdim` numbers that lie `gate_elem_off + h *
+    vdim` elements after the token's first query. Returns [T, heads * vdim] of q's type.
+    `splits` > 1: that many warps share a token's keys (decode steps)."""
+    require_cuda(q, k_cache, v_cache, positions, token_seq, block_table, q2)
+    tokens = q.shape[0]
+    _check(q.dim() == 3 and q.stride(2) == 1 and q.shape[1] == heads * maps
+           and q.shape[2] >= (q_split if q2 is not None else dim),
+           "q: [T, heads * maps, >= dim] with contiguous rows")
+    _check(k_cache.dtype == q.dtype and k_cache.is_contiguous() and k_cache.dim() == 4
+           and k_cache.shape[2] == CACHE_BLOCK, "k_cache: [blocks, kv_heads, 64, k_row] of q's type")
+    kv_heads = k_cache.shape[1]
+    _check(heads % kv_heads == 0, "heads must be a multiple of kv_heads")
+    if v_cache is not None:
+        _check(v_cache.dtype == q.dtype and v_cache.is_contiguous() and v_cache.dim() == 4
+               and v_cache.shape[1] == kv_heads and v_cache.shape[2] == CACHE_BLOCK
+               and v_cache.shape[3] >= vdim, "v_cache: [blocks, kv_heads, 64, >= vdim]")
+    else:
+        _check(k_cache.shape[3] >= vdim, "values inside the key rows: k_row >= vdim")
+    if q2 is not None:
+        _check(q2.dtype == q.dtype and q2.dim() == 3 and q2.stride(2) == 1
+               and q2.shape[:2] == q.shape[:2] and q2.shape[2] >= dim - q_split
+               and 0 <= q_split <= dim, "q2: [T, heads * maps, >= dim - q_split] of q's type")
+    _check(max(q.stride(1), 0 if q2 is None else q2.stride(1)) < 2 ** 31, "head stride too large")
+    _check(block_table.dtype == torch.int32 and block_table.dim() == 2
+           and block_table.is_contiguous(), "block_table: int32 [B, max_blocks]")
+    out = torch.empty((tokens, heads * vdim), dtype=q.dtype, device=q.device)
+    call("sakv_cached_attention", ptr(q), dtype_code(q.dtype), q.stride(0), q.stride(1), ptr(q2),
+         0 if q2 is None else q2.stride(0), 0 if q2 is None else q2.stride(1), q_split, -1,
+         ptr(out), ptr(k_cache), k_cache.shape[3], ptr(v_cache),
+         0 if v_cache is None else v_cache.shape[3], ptr(positions), ptr(token_seq),
+         ptr(block_table), block_table.shape[1], tokens, heads, kv_heads, maps, dim, vdim,
+         float(scale), int(window) if window else 0, int(chunk) if chunk else 0, float(lam),
+         float(out_scale), float(eps), -1 if gate_elem_off is None else int(gate_elem_off),
          int(splits))
     return out
 

@@ -35,6 +35,19 @@ SIGNATURES = {
     "sakv_kv_store": ("attention_distance", [P, I, L, I, I, P, P, P, I, P, P, I, I, I, I, P]),
     "sakv_distance_attention": ("attention_distance",
                                 [P, I, L, I, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, P, I, P]),
+    "sakv_cached_attention": ("attention_distance",
+                              [P, I, L, I, P, L, I, I, I, P, P, I, P, I, P, P, P, I, I, I, I, I, I,
+                               I, F, I, I, F, F, F, I, I, P]),
+    "sakv_layer_norm": ("layer_norm", [P, P, P, P, P, I, P, I, I, I, F, P]),
+    "sakv_latent_prepare": ("latent", [P, L, I, I, I, P, P, I, F, P, P, P, I, P, P, P, P, I, I, I,
+                                       P]),
+    "sakv_rotate_heads": ("latent", [P, I, L, I, I, I, I, P, P, P, I, P]),
+    "sakv_moe_route": ("moe", [P, L, I, I, P, P, P, P, I, P]),
+    "sakv_moe_plan": ("moe", [P, P, P, P, P, I, I, P]),
+    "sakv_moe_gather": ("moe", [P, I, P, P, P, P, P, P, I, I, I, I, P]),
+    "sakv_moe_product": ("moe", [P, I, P, P, L, P, P, P, P, I, P, I, I, I, F, F, P]),
+    "sakv_clamped_act": ("moe", [P, P, I, I, I, F, F, P]),
+    "sakv_moe_combine": ("moe", [P, P, P, I, P, P, L, P, I, I, I, P]),
     "sakv_rmsnorm": ("norm", [P, P, I, L, P, P, I, P, I, I, I, F, P]),
     "sakv_rope_store": ("rope", [P, I, L, P, P, P, I, P, P, I, P, P, I, I, I, I, I, P]),
     "sakv_attention_plain": ("attention_plain",
@@ -56,6 +69,7 @@ SIGNATURES = {
 #: functions without a stream argument: (library, argument types)
 PLAIN_SIGNATURES = {
     "sakv_choose_chunks": ("sampling", [I]),
+    "sakv_moe_tile_rows": ("moe", []),
     "sakv_decode_attention_map": ("attention_decode", [P, P, L, I, I]),
     "sakv_decode_attention_error": ("attention_decode", [P]),
     "sakv_decode_attention_max_cluster": ("attention_decode", [I]),

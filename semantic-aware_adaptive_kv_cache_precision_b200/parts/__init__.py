@@ -2,7 +2,7 @@
 feed-forwards and their arrangement in a block."""
 
 from .base import Part, build_part, register_part
-from .norm import RMSNorm
+from .norm import LayerNorm, RMSNorm
 from .rotary import NoPosition, RotaryHalf
 from .attention import GQAAttention
 from .mlp import DenseMLP, GatedMLP
@@ -10,7 +10,12 @@ from .block import PreNormBlock
 from .delta_rule import DeltaRuleMixer
 from .distance_attention import LogDistanceAttention
 from .streams import StreamBlock, StreamUpdate
+from .latent_attention import LatentAttention
+from .differential_attention import DifferentialAttention
+from .routed_experts import RoutedExperts
+from .sandwich import NormedUpdate, SandwichBlock
 
 __all__ = ["Part", "build_part", "register_part", "RMSNorm", "RotaryHalf", "NoPosition",
            "GQAAttention", "GatedMLP", "DenseMLP", "PreNormBlock", "DeltaRuleMixer",
-           "LogDistanceAttention", "StreamBlock", "StreamUpdate"]
+           "LogDistanceAttention", "StreamBlock", "StreamUpdate", "LayerNorm", "LatentAttention",
+           "DifferentialAttention", "RoutedExperts", "SandwichBlock", "NormedUpdate"]

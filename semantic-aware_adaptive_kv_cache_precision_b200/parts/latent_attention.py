@@ -1,0 +1,120 @@
+"""Causal attention over one cached latent a position (`LatentAttentionSpec`).
+
+    [cq | ckv | kr] = h Wdown^T;  cq = rms(cq) wq;  c = rms(ckv) wkv;  kr = rotate(kr)
+    cache <- [c | kr]                                  (kv_rank + rot_dim numbers a position)
+    q_h = [qp_h | rotate(qr_h)] = cq Wuq_h^T           (head_dim plain, rot_dim rotated)
+    s_ij = (qp_h . Wuk_h c_j + qr_h . kr_j) * scale;   out_h = Wuv_h sum_j softmax(s)_ij c_j
+
+The keys and values of a head are never made: since `qp_h . (Wuk_h c) = (Wuk_h^T qp_h) . c`,
+each head's plain query is carried into the latent's space (a batched product over the heads),
+attention runs with one shared key row [c | kr] a position for all heads and returns weighted
+sums of latents, and a second batched product takes those to the heads' values. Norms,
+rotation angles, scores, softmax weights and the weighted sums are fp32 in both modes
+(`csrc/latent.cu`, `csrc/attention_distance.cu`).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..cache.needs import KVNeed
+from ..weights.decl import TensorDecl
+from .base import Part, build_part, register_part
+
+
+class LatentAttention(Part):
+    def __init__(self, spec, prefix, mode):
+        super().__init__(spec, prefix, mode)
+        s = spec
+        if s.position.rotary_dim != s.rot_dim or s.rot_dim % 2:
+            raise ValueError(f"the rotation's {s.position.rotary_dim} dimensions must be the "
+                             f"mixer's rot_dim {s.rot_dim}, an even number")
+        if s.kv_rank + s.rot_dim > 640 or s.kv_rank > 512:
+            raise ValueError("the attention kernel takes kv_rank + rot_dim up to 640 and "
+                             "kv_rank up to 512")
+        self.position = build_part(s.position, prefix, mode)
+        self.q_width = s.head_dim + s.rot_dim
+
+    def tensor_decls(self):
+        s, p = self.spec, self.prefix
+        down = []
+        if s.q_rank:
+            down.append(TensorDecl(p + "dq", (s.q_rank, s.hidden), group=p + "down"))
+        down.append(TensorDecl(p + "dkv", (s.kv_rank + s.rot_dim, s.hidden), group=p + "down"))
+        decls = down
+        if s.q_rank:
+            decls += [TensorDecl(p + "dq.norm", (s.q_rank,), init="ones_normal"),
+                      TensorDecl(p + "uq", (s.heads * self.q_width, s.q_rank))]
+        else:
+            decls.append(TensorDecl(p + "q", (s.heads * self.q_width, s.hidden)))
+        decls += [TensorDecl(p + "dkv.norm", (s.kv_rank,), init="ones_normal"),
+                  TensorDecl(p + "uk", (s.heads * s.head_dim, s.kv_rank)),
+                  TensorDecl(p + "uv", (s.heads * s.value_dim, s.kv_rank)),
+                  TensorDecl(p + "o", (s.hidden, s.heads * s.value_dim))]
+        return decls
+
+    def bind(self, arena):
+        s, p = self.spec, self.prefix
+        self.w_down = arena.group_view(p + "down")
+        if self.w_down is None:
+            self.w_down = torch.cat([arena.view(p + n) for n in (("dq", "dkv") if s.q_rank
+                                                                 else ("dkv",))])
+        self.q_norm = arena.view(p + "dq.norm") if s.q_rank else None
+        self.w_q = arena.view(p + ("uq" if s.q_rank else "q"))
+        self.kv_norm = arena.view(p + "dkv.norm")
+        self.w_uk = arena.view(p + "uk").view(s.heads, s.head_dim, s.kv_rank)
+        self.w_uv_t = arena.view(p + "uv").view(s.heads, s.value_dim, s.kv_rank).transpose(1, 2)
+        self.w_o = arena.view(p + "o")
+
+    def prepare(self, device, max_positions):
+        self.position.prepare(device, max_positions)
+
+    def cache_need(self):
+        s = self.spec
+        return KVNeed(1, s.kv_rank + s.rot_dim, None, value_dim=0)
+
+    def produce(self, h, step, view, write_cache=True):
+        """The mixer's output, fp32 [T, hidden]."""
+        s, pos = self.spec, self.position
+        if step.max_position >= pos.cos.shape[0]:
+            raise ValueError(f"position {step.max_position} is beyond the rotary table of "
+                             f"{pos.cos.shape[0]} positions")
+        tokens, rank = h.shape[0], s.kv_rank
+        q_rank = s.q_rank or 0
+        down = ops.linear(h, self.w_down, out_dtype=torch.float32)
+        q_latent = ops.latent_prepare(down, q_rank, rank, s.rot_dim, self.q_norm, self.kv_norm,
+                                      s.eps, step, view, pos.cos, pos.sin, self.act_dtype,
+                                      write_cache)
+        q = ops.linear(q_latent if s.q_rank else h, self.w_q, out_dtype=self.act_dtype)
+        ops.rotate_heads(q, self.q_width, s.head_dim, s.heads, s.rot_dim, step.positions,
+                         pos.cos, pos.sin)
+        q3 = q.view(tokens, s.heads, self.q_width)
+        # every head's plain query in the latent's space: [heads, T, kv_rank]
+        q_latent_space = torch.bmm(q3[:, :, :s.head_dim].transpose(0, 1), self.w_uk)
+        mixed = ops.cached_attention(
+            q_latent_space.transpose(0, 1), view.keys, None, step.positions, step.token_seq,
+            view.block_table, s.heads, rank + s.rot_dim, rank, s.scale,
+            q2=q3[:, :, s.head_dim:], q_split=rank, splits=self._splits(step, q))
+        # the weighted sums of latents to each head's values: [heads, T, value_dim]
+        values = torch.bmm(mixed.view(tokens, s.heads, rank).transpose(0, 1), self.w_uv_t)
+        heads_out = values.transpose(0, 1).reshape(tokens, s.heads * s.value_dim)
+        return ops.linear(heads_out, self.w_o, out_dtype=torch.float32)
+
+    def _splits(self, step, q) -> int:
+        """How many warps share a token's keys: one in the 32-bit mode and for prompts (the
+        sums then have one order however the tokens are cut); for decode steps in bfloat16
+        one warp for every two chunks of 32 keys that a token can see, up to 16."""
+        if q.dtype == torch.float32 or not step.is_decode:
+            return 1
+        keys = step.max_len_bound or step.max_len
+        splits = 1
+        while splits < 16 and splits * 64 < keys:
+            splits *= 2
+        return splits
+
+    def forward(self, h, step, view, residual, write_cache=True):
+        ops.add_into(residual, self.produce(h, step, view, write_cache))
+
+
+register_part("latent_attention", LatentAttention)

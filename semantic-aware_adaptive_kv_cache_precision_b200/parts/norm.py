@@ -34,4 +34,33 @@ class RMSNorm(Part):
         return ops.rms_norm(x, self.weight, self.spec.eps, out_dtype, rows, add)
 
 
+class LayerNorm(RMSNorm):
+    """`(x - mean) / sqrt(variance + eps) * w` over rows of the fp32 stream, no bias; the
+    variance is the mean of the squared deviations (`csrc/layer_norm.cu`).
+
+    `forward(x, add=y, add_norm=other)` first completes the stream with a sublayer's normed
+    output, `x += other(y)`, in the same pass (`other`: the `LayerNorm` after that sublayer);
+    `complete(x, y)` does only that."""
+
+    folds_add = False            # a plain delta is added by `ops.add_into` first
+    folds_normed = True
+
+    def forward(self, x, out_dtype=None, rows=None, add=None, add_norm=None):
+        out_dtype = out_dtype or self.act_dtype
+        if add is not None and add_norm is None:
+            ops.add_into(x, add)
+            add = None
+        if add is not None and (rows is not None or add_norm.spec.eps != self.spec.eps
+                                or add_norm.weight.dtype != self.weight.dtype):
+            add_norm.complete(x, add)
+            add = None
+        return ops.layer_norm(x, self.weight, self.spec.eps, out_dtype, rows, add,
+                              None if add is None else add_norm.weight)
+
+    def complete(self, x, y):
+        """`x += norm(y)`, in place on the fp32 stream."""
+        ops.layer_norm(x, None, self.spec.eps, torch.float32, add=y, add_weight=self.weight)
+
+
 register_part("rms_norm", RMSNorm)
+register_part("layer_norm", LayerNorm)

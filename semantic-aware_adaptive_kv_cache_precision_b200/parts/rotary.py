@@ -28,12 +28,33 @@ class RotaryHalf(Part):
         n = min(max_positions, self.spec.max_positions)
         if self.cos is not None and self.cos.shape[0] >= n and self.cos.device == torch.device(device):
             return
-        rot = self.spec.rotary_dim
-        j = np.arange(rot // 2, dtype=np.float64)
-        inv_freq = np.power(float(self.spec.theta), -2.0 * j / rot)
+        inv_freq, magnitude = self.frequencies()
         angle = np.arange(n, dtype=np.float64)[:, None] * inv_freq[None, :]
-        self.cos = torch.from_numpy(np.cos(angle).astype(np.float32)).to(device)
-        self.sin = torch.from_numpy(np.sin(angle).astype(np.float32)).to(device)
+        self.cos = torch.from_numpy((np.cos(angle) * magnitude).astype(np.float32)).to(device)
+        self.sin = torch.from_numpy((np.sin(angle) * magnitude).astype(np.float32)).to(device)
+
+    def frequencies(self):
+        """(float64 [rotary_dim / 2], magnitude): pair i turns by `position * f_i`, f_i =
+        theta^(-2i / rotary_dim). With `spec.scaling` the pairs whose wavelength is long
+        against the original context turn `factor` times slower, the short ones as before,
+        a linear ramp over the pair index between the two (from the index whose wavelength
+        makes `fast` turns in `original` positions to the one that makes `slow`), and the
+        table's cosines and sines are multiplied by `magnitude_slope * ln(factor) + 1`."""
+        rot, theta = self.spec.rotary_dim, float(self.spec.theta)
+        j = np.arange(rot // 2, dtype=np.float64)
+        inv_freq = np.power(theta, -2.0 * j / rot)
+        sc = getattr(self.spec, "scaling", None)
+        if sc is None:
+            return inv_freq, 1.0
+
+        def pair_with(turns):
+            return rot * np.log(sc.original / (2.0 * np.pi * turns)) / (2.0 * np.log(theta))
+
+        low = max(np.floor(pair_with(sc.fast)), 0.0)
+        high = min(np.ceil(pair_with(sc.slow)), rot - 1.0)
+        ramp = np.clip((j - low) / max(high - low, 0.001), 0.0, 1.0)
+        stretched = inv_freq / sc.factor * ramp + inv_freq * (1.0 - ramp)
+        return stretched, sc.magnitude_slope * np.log(sc.factor) + 1.0
 
     def tables(self, step, head_dim):
         """(cos, sin) for a kernel that rotates on its own way (the decode attention), or None
