@@ -12,7 +12,7 @@ import torch
 
 from ._lib import (BF16, CACHE_BLOCK, F32, KernelError, call, dtype_code, plain_function, ptr,
                    require_cuda)
-from .linear import Deferred, gated_up, linear
+from .linear import Deferred, gated_up, linear, per_head
 from . import gemm_tc
 from .streams import streams_spread, streams_step, token_shift
 from .recurrent import delta_rule
@@ -29,7 +29,7 @@ __all__ = ["CACHE_BLOCK", "KernelError", "embed", "rms_norm", "rope_store", "att
            "decode_splits", "fast_path_takes", "forget_descriptors",
            "kernel_errors", "gated_silu", "gelu_tanh", "streams_step", "streams_spread", "token_shift",
            "delta_rule", "kv_store", "layer_norm", "cached_attention", "mixture", "latent_prepare",
-           "rotate_heads", "distance_attention", "gated_up", "gemm_tc", "add_into", "scale_cap_", "linear", "choose", "Deferred"]
+           "rotate_heads", "distance_attention", "gated_up", "gemm_tc", "add_into", "scale_cap_", "linear", "per_head", "choose", "Deferred"]
 
 
 def _check(cond: bool, message: str) -> None:

@@ -85,6 +85,31 @@ def gated_up(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
     return gated_silu(linear(x, w_gate_up, out_dtype=x.dtype))
 
 
+def per_head(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """A product a head: `out[:, h] = x[:, h] weight[h]^T` for x [T, heads, K], weight [heads,
+    N, K] (contiguous) and out [T, heads, N], both views with any strides between tokens and
+    heads (slices of projections' outputs). float32: the true 32-bit product head by head, each
+    row's sums in one order whatever else is in the step; bfloat16: the library's batched
+    product."""
+    require_cuda(x, weight, out)
+    heads, n, k = weight.shape
+    if x.dim() != 3 or out.dim() != 3 or x.shape[1:] != (heads, k) or out.shape[1:] != (heads, n) \
+            or x.shape[0] != out.shape[0] or x.stride(2) != 1 or out.stride(2) != 1 \
+            or not weight.is_contiguous() or x.dtype != weight.dtype or out.dtype != weight.dtype:
+        raise KernelError(f"per_head: x {tuple(x.shape)}, weight {tuple(weight.shape)} and out "
+                          f"{tuple(out.shape)} do not fit")
+    tokens = x.shape[0]
+    if tokens == 0:
+        return out
+    if weight.dtype == torch.float32:
+        for h in range(heads):
+            call("sakv_gemm_f32", x[:, h].data_ptr(), x.stride(0), weight[h].data_ptr(), None,
+                 out[:, h].data_ptr(), out.stride(0), tokens, n, k, 0)
+        return out
+    torch.bmm(x.transpose(0, 1), weight.transpose(1, 2), out=out.transpose(0, 1))
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, *,
            out_dtype: torch.dtype | None = None,
            accumulate_into: torch.Tensor | None = None, may_defer: bool = False):

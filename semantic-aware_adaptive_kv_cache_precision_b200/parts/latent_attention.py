@@ -60,11 +60,15 @@ class LatentAttention(Part):
         if self.w_down is None:
             self.w_down = torch.cat([arena.view(p + n) for n in (("dq", "dkv") if s.q_rank
                                                                  else ("dkv",))])
-        self.q_norm = arena.view(p + "dq.norm") if s.q_rank else None
+        # (the small tensors below take the activations' type whatever the checkpoint's)
+        self.q_norm = arena.view(p + "dq.norm").to(self.act_dtype) if s.q_rank else None
         self.w_q = arena.view(p + ("uq" if s.q_rank else "q"))
-        self.kv_norm = arena.view(p + "dkv.norm")
-        self.w_uk = arena.view(p + "uk").view(s.heads, s.head_dim, s.kv_rank)
-        self.w_uv_t = arena.view(p + "uv").view(s.heads, s.value_dim, s.kv_rank).transpose(1, 2)
+        self.kv_norm = arena.view(p + "dkv.norm").to(self.act_dtype)
+        # [heads, kv_rank, head_dim]: the rows of Wuk_h^T, which carry a plain query to the
+        # latent's space (a small copy, made once)
+        self.w_uk_t = arena.view(p + "uk").view(s.heads, s.head_dim, s.kv_rank) \
+            .transpose(1, 2).to(self.act_dtype).contiguous()
+        self.w_uv = arena.view(p + "uv").view(s.heads, s.value_dim, s.kv_rank).to(self.act_dtype)
         self.w_o = arena.view(p + "o")
 
     def prepare(self, device, max_positions):
@@ -90,16 +94,18 @@ class LatentAttention(Part):
         ops.rotate_heads(q, self.q_width, s.head_dim, s.heads, s.rot_dim, step.positions,
                          pos.cos, pos.sin)
         q3 = q.view(tokens, s.heads, self.q_width)
-        # every head's plain query in the latent's space: [heads, T, kv_rank]
-        q_latent_space = torch.bmm(q3[:, :, :s.head_dim].transpose(0, 1), self.w_uk)
+        # every head's plain query in the latent's space
+        in_latent = torch.empty((tokens, s.heads, rank), dtype=q.dtype, device=q.device)
+        ops.per_head(q3[:, :, :s.head_dim], self.w_uk_t, in_latent)
         mixed = ops.cached_attention(
-            q_latent_space.transpose(0, 1), view.keys, None, step.positions, step.token_seq,
-            view.block_table, s.heads, rank + s.rot_dim, rank, s.scale,
-            q2=q3[:, :, s.head_dim:], q_split=rank, splits=self._splits(step, q))
-        # the weighted sums of latents to each head's values: [heads, T, value_dim]
-        values = torch.bmm(mixed.view(tokens, s.heads, rank).transpose(0, 1), self.w_uv_t)
-        heads_out = values.transpose(0, 1).reshape(tokens, s.heads * s.value_dim)
-        return ops.linear(heads_out, self.w_o, out_dtype=torch.float32)
+            in_latent, view.keys, None, step.positions, step.token_seq, view.block_table,
+            s.heads, rank + s.rot_dim, rank, s.scale, q2=q3[:, :, s.head_dim:], q_split=rank,
+            splits=self._splits(step, q))
+        # the weighted sums of latents to each head's values
+        heads_out = torch.empty((tokens, s.heads, s.value_dim), dtype=q.dtype, device=q.device)
+        ops.per_head(mixed.view(tokens, s.heads, rank), self.w_uv, heads_out)
+        return ops.linear(heads_out.view(tokens, s.heads * s.value_dim), self.w_o,
+                          out_dtype=torch.float32)
 
     def _splits(self, step, q) -> int:
         """How many warps share a token's keys: one in the 32-bit mode and for prompts (the

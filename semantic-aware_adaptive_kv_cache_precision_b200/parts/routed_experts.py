@@ -84,7 +84,9 @@ class RoutedExperts(Part):
         logits = ops.linear(h if h.dtype == torch.float32 else h.float(), self.w_route,
                             out_dtype=torch.float32)
         routing = mixture.route(logits, s.experts, s.top)
-        rows = mixture.gather_rows(h, routing, s.weight_input)
+        # (a checkpoint stored in 32 bits keeps its matrices so: the experts then run in 32 bits)
+        rows = mixture.gather_rows(h if h.dtype == self.w_gate.dtype else h.to(self.w_gate.dtype),
+                                   routing, s.weight_input)
         act = mixture.grouped_product(rows, routing, self.w_gate, self.w_up, s.expert.limit,
                                       s.expert.alpha)
         products = mixture.grouped_product(act, routing, self.w_down, None)

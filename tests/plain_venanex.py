@@ -17,7 +17,7 @@ from plain_model import read_model_folder      # the tests' own safetensors read
 
 __all__ = ["read_model_folder", "layer_norm", "rms_norm", "sigmoid", "yarn_frequencies",
            "rotate_half", "softmax_rows", "latent_attention", "differential_attention",
-           "expert", "routed_experts", "moe", "layer", "run_order", "forward", "generate"]
+           "expert", "routed_experts", "router_margins", "moe", "layer", "run_order", "forward", "generate"]
 
 
 def layer_norm(x, w, eps):
@@ -81,8 +81,11 @@ def latent_attention(h, t, p, m, eps):
     n = h.shape[0]
     H, D, R, Dv, C = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     pos = np.arange(n)
-    cq = rms_norm(h @ t[p + "dq"].T, t[p + "dq.norm"], eps)
-    q = (cq @ t[p + "uq"].T).reshape(n, H, D + R)
+    if m.get("q_rank"):
+        cq = rms_norm(h @ t[p + "dq"].T, t[p + "dq.norm"], eps)
+        q = (cq @ t[p + "uq"].T).reshape(n, H, D + R)
+    else:                                     # no query latent: straight from the input
+        q = (h @ t[p + "q"].T).reshape(n, H, D + R)
     q_plain, q_rot = q[..., :D], rotate_half(q[..., D:], pos, m["rot"])
     down = h @ t[p + "dkv"].T
     c = rms_norm(down[:, :C], t[p + "dkv.norm"], eps)
@@ -101,7 +104,8 @@ def differential_attention(h, t, p, m, eps):
     """Two softmax maps a head over the same values, o = a1 - lambda a2, unit norm a head,
     (1 - diff), an output gate from the mixer's own input."""
     n = h.shape[0]
-    H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, D = m["heads"], m["dim"]
+    G, Dv = m.get("kv_heads", H), m.get("vdim", D)
     q = (h @ t[p + "q"].T).reshape(n, H, 2, D)
     k = (h @ t[p + "k"].T).reshape(n, G, 2, D)
     v = (h @ t[p + "v"].T).reshape(n, G, Dv)
@@ -135,9 +139,19 @@ def routed_experts(h, t, p, experts, top):
     return chosen, np.take_along_axis(s, chosen, -1)
 
 
-def moe(h, t, p, m):
+def router_margins(h, t, p, experts, top):
+    """For each token, how far the last chosen expert's logit lies above the best one left
+    out (inf when every expert is chosen): a small margin is a close call that rounding may
+    turn."""
+    z = np.sort(h @ t[p + "router"].T, axis=-1)[:, ::-1]
+    return z[:, top - 1] - z[:, top] if top < experts else np.full(h.shape[0], np.inf)
+
+
+def moe(h, t, p, m, margins=None):
     n = h.shape[0]
     chosen, weights = routed_experts(h, t, p, m["router"]["experts"], m["router"]["top"])
+    if margins is not None:
+        margins.append(router_margins(h, t, p, m["router"]["experts"], m["router"]["top"]))
     out = np.zeros((n, t[p + "e0.down"].shape[0]))
     for i in range(n):
         for e, w in zip(chosen[i], weights[i]):       # the weight multiplies the expert's INPUT
@@ -147,7 +161,7 @@ def moe(h, t, p, m):
     return out
 
 
-def layer(x, t, i, entry, eps):
+def layer(x, t, i, entry, eps, margins=None):
     p = f"l{i}."
     h = layer_norm(x, t[p + "norm1"], eps)
     if entry["type"] == "latent_attention":
@@ -158,7 +172,7 @@ def layer(x, t, i, entry, eps):
         raise ValueError(entry["type"])
     x = x + layer_norm(y, t[p + "norm1b"], eps)
     if entry.get("mlp") is not None:
-        y = moe(layer_norm(x, t[p + "norm2"], eps), t, p + "mlp.", entry["mlp"])
+        y = moe(layer_norm(x, t[p + "norm2"], eps), t, p + "mlp.", entry["mlp"], margins)
         x = x + layer_norm(y, t[p + "norm2b"], eps)
     return x
 
@@ -174,16 +188,17 @@ def run_order(config):
     return order + [(i, False) for i in range(loop["stop"], n)]
 
 
-def forward(config, t, ids, layers_out=None):
+def forward(config, t, ids, layers_out=None, margins=None):
     """Logits [n, vocab] of a whole sequence; `layers_out` (a list) receives the residual
-    stream after every layer run."""
+    stream after every layer run, `margins` (a list) every routed layer run's
+    `router_margins`."""
     eps = config["norm"]["eps"]
     x0 = t["embed"][np.asarray(ids)]
     x = x0.copy()
     for i, first in run_order(config):
         if first:
             x = np.concatenate([x, x0], axis=-1) @ t["loop.in"].T
-        x = layer(x, t, i, config["layers"][i], eps)
+        x = layer(x, t, i, config["layers"][i], eps, margins)
         if layers_out is not None:
             layers_out.append(x.copy())
     return layer_norm(x, t["final.norm"], eps) @ t["embed"].T
