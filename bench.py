@@ -365,6 +365,90 @@ DESIGN_SIZES = {
 }
 
 
+#: layer sizes for `--design venanex`: (width, latent attention heads x (plain, rotated, value)
+#: sizes over a latent of kv_rank and a query latent of q_rank, two-map attention heads / kv
+#: heads x (dim, vdim) in chunks, experts: count, chosen, width, shared width)
+VENANEX_SIZES = {
+    "1k": dict(width=1024, latent=(8, 128, 64, 128), kv_rank=512, q_rank=384,
+               attention=(4, 2, 128, 256), chunk=1024, experts=(16, 2, 1024, 2048), vocab=32768,
+               layers=6),
+    "2k": dict(width=2048, latent=(16, 128, 64, 128), kv_rank=512, q_rank=768,
+               attention=(8, 2, 128, 256), chunk=2048, experts=(32, 4, 1024, 4096), vocab=32768,
+               layers=6),
+}
+
+
+def venanex_configs(size: dict) -> tuple:
+    """(Venanex config, the Qwen2 config of equal width and depth, with as many query columns
+    and as wide a feed-forward as a Venanex token uses)."""
+    heads, dim, rot, vdim = size["latent"]
+    aheads, akv, adim, avdim = size["attention"]
+    experts, top, ff, shared = size["experts"]
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top},
+           "expert": {"ff": ff, "limit": 7.0}, "shared": {"ff": shared, "limit": 7.0}}
+    layers = []
+    for i in range(size["layers"]):
+        if i % 3 == 2:
+            mixer = {"heads": aheads, "kv_heads": akv, "dim": adim, "vdim": avdim,
+                     "scale": adim ** -0.5, "diff": 0.3, "mask": {"size": size["chunk"]}}
+            kind = "attention"
+        else:
+            mixer = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim,
+                     "kv_rank": size["kv_rank"], "q_rank": size["q_rank"],
+                     "scale": (dim + rot) ** -0.5,
+                     "rot": {"base": 10000.0, "dims": rot,
+                             "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+            kind = "latent_attention"
+        layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    venanex = {"architecture": "Venanex", "vocab": size["vocab"], "width": size["width"],
+               "norm": {"eps": 1e-6}, "initializer_range": 0.02, "layers": layers,
+               "loop": {"start": 0, "stop": 3, "times": 1}}
+    qwen2 = {**QWEN25_1P5B, "num_hidden_layers": size["layers"], "hidden_size": size["width"],
+             "num_attention_heads": heads, "num_key_value_heads": max(heads // 4, 1),
+             "head_dim": 128, "intermediate_size": top * ff + shared, "vocab_size": size["vocab"],
+             "tie_word_embeddings": True}
+    return venanex, qwen2
+
+
+def venanex_rates(size, times, batch, context, tokens, hbm) -> dict:
+    """What the design's own kernels must move or compute in the timed steps, against the
+    measured peaks: fp32 multiply-adds of the two attentions over a prompt, bytes of cache
+    that a decode step reads, bf16 multiply-adds of the experts' grouped products over a
+    prompt and the bytes of expert weights a decode step can touch, bytes of the norms."""
+    heads, dim, rot, vdim = size["latent"]
+    aheads, akv, adim, avdim = size["attention"]
+    experts, top, ff, shared = size["experts"]
+    n_att = sum(1 for i in range(size["layers"]) if i % 3 == 2)
+    n_lat = size["layers"] - n_att
+    rank, width = size["kv_rank"], size["width"]
+    pairs = tokens * (tokens + 1) // 2
+    chunk_pairs = sum(i % size["chunk"] + 1 for i in range(tokens))
+    flops = 2.0 * heads * (2 * rank + rot) * pairs * n_lat + \
+        2.0 * aheads * (2 * adim + 2 * avdim) * chunk_pairs * n_att
+    out = {}
+    if times["prefill"].get("cached_attention"):
+        out["attention_prefill_tflops_fp32"] = round(
+            flops / (times["prefill"]["cached_attention"] * 1e-6) / 1e12, 2)
+    if times["decode"].get("cached_attention"):
+        seen = min(context, size["chunk"])          # (an upper bound for the chunked layers)
+        read = batch * 2 * (context * (rank + rot) * n_lat + seen * akv * (2 * adim + avdim) * n_att)
+        out["attention_decode_of_measured_hbm"] = round(
+            read / (times["decode"]["cached_attention"] * 1e-6) / 1e9 / hbm, 3)
+    if times["prefill"].get("moe_product"):
+        flops = 2.0 * tokens * top * 3 * ff * width * size["layers"]
+        out["experts_prefill_tflops_bf16"] = round(
+            flops / (times["prefill"]["moe_product"] * 1e-6) / 1e12, 2)
+    if times["decode"].get("moe_product"):
+        touched = min(batch * top, experts) * 3 * ff * width * 2 * size["layers"]
+        out["experts_decode_of_measured_hbm"] = round(
+            touched / (times["decode"]["moe_product"] * 1e-6) / 1e9 / hbm, 3)
+    if times["prefill"].get("layer_norm"):          # two passes a layer: y and x in, x and h out
+        moved = tokens * width * (4 + 4 + 4 + 2) * 2 * size["layers"]
+        out["layer_norm_prefill_of_measured_hbm"] = round(
+            moved / (times["prefill"]["layer_norm"] * 1e-6) / 1e9 / hbm, 3)
+    return out
+
+
 def design_configs(size: dict) -> tuple:
     """(Tebonex config, the Qwen2 config of equal width, depth, heads and feed-forward)."""
     heads, kv_heads, dim = size["attention"]
@@ -488,6 +572,33 @@ def design_arm(args) -> int:
             _lib.function = real
         return out
 
+    if args.design == "venanex":
+        for name in sizes:
+            size = VENANEX_SIZES[name]
+            venanex, qwen2 = venanex_configs(size)
+            row = {"size": name, **{k: size[k] for k in ("width", "layers", "kv_rank", "chunk",
+                                                         "experts")}}
+            for label, config in (("qwen2", qwen2), ("venanex", venanex)):
+                engine, slots, prompt, out = measure(config)
+                row[label] = out
+                engine.close(slots)
+                engine.release()
+                del engine
+                torch.cuda.empty_cache()
+            engine, slots, prompt, _ = measure(venanex, graphs=False)
+            row["venanex_kernels_us"] = times = kernel_times(engine, slots, prompt)
+            row["venanex_kernel_rates"] = venanex_rates(size, times, batch, context, tokens, hbm)
+            engine.close(slots)
+            engine.release()
+            del engine
+            torch.cuda.empty_cache()
+            rows.append(row)
+        print(json.dumps({"design": "venanex", "beside": "qwen2 of equal width and depth, with "
+                          "the feed-forward width a Venanex token uses", "dtype": "bf16",
+                          "data": "synthetic (random weights and tokens; weights larger than L2)",
+                          "batch": batch, "context": context, "prefill_tokens": tokens, "steps": K,
+                          "warmup": W, "peaks": pk, "sizes": rows}))
+        return 0
     for name in sizes:
         size = DESIGN_SIZES[name]
         tebonex, qwen2 = design_configs(size)
@@ -544,7 +655,7 @@ def design_arm(args) -> int:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default=None, choices=["tebonex"],
+    ap.add_argument("--design", default=None, choices=["tebonex", "venanex"],
                     help="instead of the default workload: the named design at layer sizes "
                          "that resemble real models, beside the Qwen2 decoder of equal size")
     ap.add_argument("--design-sizes", default="1k,2k", help="which of: " + ", ".join(DESIGN_SIZES))

@@ -42,6 +42,14 @@ struct AttentionExtra {
   int gate_elem_off;         // column of the element-wise gate in qkv (-1: none)
   int no_trigger;            // the kernel after this one may be a library's: it starts only
                              // when this one has completed
+  // A token's keys over `key_splits` blocks (grid y) as well as over a block's warps: every
+  // block leaves its sums in `scratch`, takes a ticket, and the block that takes a token's
+  // last ticket folds them in the order of the splits and writes the output.
+  int key_splits;
+  float* scratch;            // [items, key_splits, P, row_floats]
+  long long scratch_floats;
+  int* tickets;              // [items], zero on entry and on exit
+  int warp_stage;            // decode: every warp copies its chunks into shared memory first
 };
 
 namespace {
@@ -198,7 +206,7 @@ __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, flo
 }
 
 template <int P, int VPL, int MAPS, typename T>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(VPL >= 16 ? 256 : 512)      // (wide values: more registers)
 distance_attention_tiled_kernel(
     const T* __restrict__ qkv, long long stride, int gate_off, T* __restrict__ out,
     const T* __restrict__ k_cache, const T* __restrict__ v_cache,
@@ -284,14 +292,16 @@ distance_attention_tiled_kernel(
 #pragma unroll
        for (int mm = 0; mm < MAPS; ++mm, kp += dim) {        // a map's key in the key row
         if (wide_k) {
-          // four 16-byte pieces of the key's row are asked for before any is used
-          for (int e = 0; e < dim; e += 32) {
-            float kv[4][8];
+          // four 16-byte pieces of the key's row are asked for before any is used (eight were
+          // slower for the widest rows: 6.8 against 9.7 TFLOP/s over a prompt)
+          constexpr int kAhead = 4;
+          for (int e = 0; e < dim; e += 8 * kAhead) {
+            float kv[kAhead][8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < kAhead; ++i)
               if (e + 8 * i < dim) load8<T>(kp + e + 8 * i, kv[i]);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < kAhead; ++i) {
               if (e + 8 * i < dim) {
 #pragma unroll
                 for (int p = mm; p < P; p += MAPS) {
@@ -384,8 +394,36 @@ distance_attention_tiled_kernel(
       return ((long long)table[c >> 1] * kv_heads + g) * kCacheBlock + (c & 1) * 32;
     };
     if (!staged) {
-      for (int c = first / 32 + split; c <= pos / 32; c += splits) {
+      const int c0 = first / 32 + (x.key_splits > 1 ? (int)blockIdx.y * splits : 0) + split;
+      for (int c = c0; c <= pos / 32; c += splits * (x.key_splits > 1 ? x.key_splits : 1)) {
         const long long rows = rows_of(c);
+        if (stage_ok == 2) {
+          // a decoded token: the warp copies its chunk's rows into shared memory with every
+          // copy in flight at once (one trip to memory a chunk instead of one every few
+          // pieces of a row), then scores from there
+          constexpr int kPiece = 16 / (int)sizeof(T);
+          const int kstride = k_row + kPiece;
+          const int per_warp = 32 * (kstride + (x.v_in_k ? 0 : vdim));
+          T* ks = reinterpret_cast<T*>(shared + (long long)warps * P * row_floats) +
+                  (long long)warp * per_warp;
+          T* vs = ks + 32 * kstride;
+          const int kp16 = k_row / kPiece, vp16 = x.v_in_k ? 0 : vdim / kPiece;
+          for (int i = lane; i < 32 * kp16; i += 32) {
+            const int r = i / kp16, q = (i - r * kp16) * kPiece;
+            copy16_async(ks + r * kstride + q, k_cache + (rows + r) * k_row + q);
+          }
+          for (int i = lane; i < 32 * vp16; i += 32) {
+            const int r = i / vp16, q = (i - r * vp16) * kPiece;
+            copy16_async(vs + r * vdim + q, v_cache + (rows + r) * v_row + q);
+          }
+          copies_commit();
+          asm volatile("cp.async.wait_group 0;" ::: "memory");
+          __syncwarp();
+          if (x.v_in_k) chunk(c, ks + lane * kstride, ks + lane * VPL, kstride);
+          else chunk(c, ks + lane * kstride, vs + lane * VPL, vdim);
+          __syncwarp();
+          continue;
+        }
         chunk(c, k_cache + (rows + lane) * k_row, v_cache + rows * v_row + lane * VPL, v_row);
       }
     } else {
@@ -455,15 +493,59 @@ distance_attention_tiled_kernel(
       for (int i = 0; i < VPL; ++i) sum[i] = 0.f;
       for (int w = 0; w < splits; ++w) {
         const float* row = shared + ((long long)(warp + w) * P + p) * row_floats;
-        const float f = expf(row[0] - top);
+        const float f = row[0] == -INFINITY ? 0.f : expf(row[0] - top);   // (a warp without keys)
         total = fmaf(row[1], f, total);
 #pragma unroll
         for (int i = 0; i < VPL; ++i)
           if (lane * VPL + i < vdim) sum[i] = fmaf(row[2 + lane * VPL + i], f, sum[i]);
       }
+      m[p] = top;
       l[p] = total;
 #pragma unroll
       for (int i = 0; i < VPL; ++i) acc[p][i] = sum[i];
+    }
+    if (x.key_splits > 1) {              // (uniform over the grid; this warp is the item's)
+      const int S = x.key_splits;
+      float* part = x.scratch + ((item * S + blockIdx.y) * P) * (long long)row_floats;
+#pragma unroll
+      for (int p = 0; p < P; ++p) {
+        float* row = part + (long long)p * row_floats;
+        if (lane == 0) {
+          row[0] = m[p];
+          row[1] = l[p];
+        }
+#pragma unroll
+        for (int i = 0; i < VPL; ++i)
+          if (lane * VPL + i < vdim) row[2 + lane * VPL + i] = acc[p][i];
+      }
+      __threadfence();
+      int ticket = 0;
+      if (lane == 0) ticket = atomicAdd(x.tickets + item, 1);
+      ticket = __shfl_sync(0xffffffffu, ticket, 0);
+      if (ticket != S - 1) return;
+      __threadfence();
+      if (lane == 0) x.tickets[item] = 0;
+      const float* all = x.scratch + (item * S * P) * (long long)row_floats;
+#pragma unroll
+      for (int p = 0; p < P; ++p) {
+        float top = -INFINITY;
+        for (int w = 0; w < S; ++w) top = fmaxf(top, __ldcg(all + ((long long)w * P + p) * row_floats));
+        float total = 0.f, sum[VPL];
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) sum[i] = 0.f;
+        for (int w = 0; w < S; ++w) {
+          const float* row = all + ((long long)w * P + p) * row_floats;
+          const float mw = __ldcg(row);
+          const float f = mw == -INFINITY ? 0.f : expf(mw - top);
+          total = fmaf(__ldcg(row + 1), f, total);
+#pragma unroll
+          for (int i = 0; i < VPL; ++i)
+            if (lane * VPL + i < vdim) sum[i] = fmaf(__ldcg(row + 2 + lane * VPL + i), f, sum[i]);
+        }
+        l[p] = total;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) acc[p][i] = sum[i];
+      }
     }
   }
   if (!active) return;
@@ -532,6 +614,7 @@ int launch_tiled(const void* qkv, long long stride, int gate_off, void* out, con
   int row_floats = (dim > vdim + 2 ? dim : vdim + 2);
   row_floats = (row_floats + 3) / 4 * 4;                     // rows stay 16-byte aligned
   int warps = splits > 1 ? splits : (tokens >= 64 ? 8 : 4);     // (a block's tokens share keys)
+  if (VPL >= 16 && warps > 8) warps = 8;                        // (the kernel's launch bounds)
   while ((size_t)warps * P * row_floats * sizeof(float) > (size_t)kBudget && warps > 1) warps /= 2;
   if ((size_t)warps * P * row_floats * sizeof(float) > (size_t)kBudget) return cudaErrorInvalidValue;
   if (splits > 1) splits = warps;
@@ -539,16 +622,29 @@ int launch_tiled(const void* qkv, long long stride, int gate_off, void* out, con
   size_t smem = (size_t)warps * P * row_floats * sizeof(float);
   const size_t staging =
       (size_t)2 * 32 * (x.k_row + 16 / sizeof(T) + (x.v_in_k ? 0 : vdim)) * sizeof(T);
-  const int stage_ok = splits == 1 && warps >= 4 && tokens >= warps &&
-                       (x.k_row * sizeof(T)) % 16 == 0 && (vdim * sizeof(T)) % 16 == 0 &&
-                       (x.v_row * sizeof(T)) % 16 == 0 &&
-                       !((uintptr_t)k_cache & 15) && !((uintptr_t)v_cache & 15) &&
-                       smem + staging <= (size_t)kBudget;
+  const bool copies_fit = (x.k_row * sizeof(T)) % 16 == 0 && (vdim * sizeof(T)) % 16 == 0 &&
+                          (x.v_row * sizeof(T)) % 16 == 0 && !((uintptr_t)k_cache & 15) &&
+                          !((uintptr_t)v_cache & 15);
+  int stage_ok = splits == 1 && warps >= 4 && tokens >= warps && copies_fit &&
+                 smem + staging <= (size_t)kBudget;
   if (stage_ok) smem += staging;
+  // a decoded token's warps: a chunk's rows a warp (`stage_ok` 2), where the step asked for it
+  if (splits > 1 && x.warp_stage && copies_fit &&
+      smem + (staging / 2) * warps <= (size_t)kBudget) {
+    stage_ok = 2;
+    smem += (staging / 2) * warps;
+  }
   const long long items = (long long)tokens * kv_heads * per_group;
   const long long blocks = (items + warps / splits - 1) / (warps / splits);
   if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
-  return launch_overlapped(kernel, dim3((unsigned)blocks), dim3(warps * 32), smem, stream, 1,
+  unsigned across = 1;
+  if (x.key_splits > 1) {
+    if (splits <= 1 || x.key_splits > 64 || x.scratch == nullptr || x.tickets == nullptr ||
+        items * x.key_splits * P * row_floats > x.scratch_floats)
+      return cudaErrorInvalidValue;
+    across = (unsigned)x.key_splits;
+  }
+  return launch_overlapped(kernel, dim3((unsigned)blocks, across), dim3(warps * 32), smem, stream, 1,
                            (const T*)qkv, stride, gate_off, (T*)out, (const T*)k_cache,
                            (const T*)v_cache, positions, token_seq, block_table, max_blocks,
                            tokens, heads, kv_heads, dim, vdim, scale, window, slope, rate, splits,
@@ -684,7 +780,10 @@ SAKV_EXPORT int sakv_distance_attention(const void* qkv, int dtype, long long st
 // `window` and `chunk` exclude each other. With two maps: lambda, out_scale, eps and
 // gate_elem_off (the element-wise gate's first column in qkv, -1 for none) shape the output;
 // with one map `gate_off` is the gate a head as above. out: [tokens, heads * vdim].
-// `splits` >= 1 as above.
+// `splits` >= 1 as above. `key_splits` > 1 (with splits > 1): that many blocks share a token's
+// keys as well; `scratch` (floats, at least tokens * kv_heads * (heads * maps / kv_heads + 3) *
+// key_splits * (max(dim, vdim + 2) + 4)) holds their sums and `tickets` (int32 for every
+// token, kv head and group of heads; zero on entry, left zero) tells which block came last.
 SAKV_EXPORT int sakv_cached_attention(
     const void* qkv, int dtype, long long stride, int q_head_stride, const void* q2,
     long long q2_stride, int q2_head_stride, int q_split, int gate_off, void* out,
@@ -692,7 +791,8 @@ SAKV_EXPORT int sakv_cached_attention(
     const int32_t* positions, const int32_t* token_seq, const int32_t* block_table,
     int max_blocks, int tokens, int heads, int kv_heads, int maps, int dim, int vdim, float scale,
     int window, int chunk, float lambda, float out_scale, float eps, int gate_elem_off,
-    int splits, cudaStream_t stream) {
+    int splits, int key_splits, float* scratch, long long scratch_floats, int* tickets,
+    int warp_stage, cudaStream_t stream) {
   if (tokens < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || vdim <= 0 ||
       dim > 640 || vdim > 512 || max_blocks <= 0 || window < 0 || chunk < 0 ||
       (window > 0 && chunk > 0) || splits < 1 || splits > 16 || (maps != 1 && maps != 2) ||
@@ -716,6 +816,11 @@ SAKV_EXPORT int sakv_cached_attention(
   x.eps = eps;
   x.gate_elem_off = gate_elem_off;
   x.no_trigger = 1;
+  x.key_splits = key_splits > 1 ? key_splits : 1;
+  x.scratch = scratch;
+  x.scratch_floats = scratch_floats;
+  x.tickets = tickets;
+  x.warp_stage = warp_stage;
   const void* values = x.v_in_k ? k_cache : v_cache;
   if (dtype == SAKV_F32)
     return pick_tiled<float>(qkv, stride, gate_off, out, k_cache, values, positions, token_seq,

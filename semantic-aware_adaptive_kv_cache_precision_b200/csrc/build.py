@@ -171,6 +171,18 @@ def build_all(verbose: bool = True, jobs: int | None = None) -> None:
             pass
 
 
+def build_many(names, verbose: bool = True) -> None:
+    """Compile those of the libraries `names` that are missing or stale, side by side (a
+    model's first load then waits for its slowest source, not for the sum of them)."""
+    from concurrent.futures import ThreadPoolExecutor
+    names = [n for n in dict.fromkeys(names) if n in LIBRARIES and not is_built(n)]
+    if not names:
+        return
+    with ThreadPoolExecutor(max_workers=min(8, len(names))) as pool:
+        for _ in pool.map(lambda n: build(n, verbose), names):
+            pass
+
+
 _loaded: dict[str, ctypes.CDLL] = {}
 
 

@@ -26,6 +26,24 @@ constexpr int TM = 32;          // rows of a tile
 constexpr int TN = 64;          // output columns of a tile
 constexpr int TK = 32;          // K step
 
+// Router logits in fp32: a warp a (token, output) walks the row; the order of the sums
+// depends on the width alone.
+template <typename T>
+__global__ void logits_kernel(const T* __restrict__ h, const float* __restrict__ w,
+                              float* __restrict__ out, int outputs, int width, long long count) {
+  const long long item = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (item >= count) return;
+  const long long t = item / outputs;
+  const int o = static_cast<int>(item - t * outputs);
+  const T* x = h + t * width;
+  const float* row = w + (long long)o * width;
+  float sum = 0.f;
+  for (int i = lane; i < width; i += 32) sum = fmaf(widen(x[i]), row[i], sum);
+  sum = warp_sum(sum);
+  if (lane == 0) out[item] = sum;
+}
+
 __global__ void route_kernel(const float* __restrict__ logits, long long ld, int experts, int top,
                              int32_t* __restrict__ chosen, float* __restrict__ weights,
                              int32_t* __restrict__ counts, int32_t* __restrict__ rank,
@@ -178,6 +196,116 @@ grouped_kernel(const T* __restrict__ a, const T* __restrict__ w0, const T* __res
   }
 }
 
+// The same tile on the tensor cores (bf16 operands, fp32 accumulators: `mma.sync` m16n8k16).
+// 128 threads; warp w owns output columns [16 w, 16 w + 16) of the tile's 64 for all 32 rows.
+// Rows and weights come through a ring of three or four shared-memory stages filled by 16-byte
+// asynchronous copies, rows padded to 80 bytes so that the 8 x 16-byte reads of an `ldmatrix`
+// fall into different banks. Rows beyond the expert's last and columns beyond n are zeros.
+constexpr int kPad = 40;                 // bf16 elements in a padded row of TK = 32
+
+__device__ __forceinline__ void copy16(void* dst, const void* src, bool real) {
+  const uint32_t to = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+  const int bytes = real ? 16 : 0;       // (0: the 16 bytes are filled with zeros)
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(to), "l"(src), "r"(bytes)
+               : "memory");
+}
+
+template <bool DUAL>
+__global__ void __launch_bounds__(128)
+grouped_tc_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w0,
+                  const __nv_bfloat16* __restrict__ w1, long long expert_stride,
+                  const int32_t* __restrict__ tile_expert, const int32_t* __restrict__ tile_row,
+                  const int32_t* __restrict__ offsets, const int32_t* __restrict__ n_tiles,
+                  void* __restrict__ out_v, int n, int k, float limit, float alpha) {
+  constexpr int kW = DUAL ? 2 : 1;
+  constexpr int kStages = DUAL ? 3 : 4;          // (48 KB of static shared memory at most)
+  __shared__ __align__(16) __nv_bfloat16 as[kStages][TM][kPad];
+  __shared__ __align__(16) __nv_bfloat16 ws[kStages][kW][TN][kPad];
+  if ((int)blockIdx.x >= *n_tiles) return;
+  const int e = tile_expert[blockIdx.x], row0 = tile_row[blockIdx.x];
+  const int row_end = offsets[e + 1];
+  const int n0 = blockIdx.y * TN;
+  const __nv_bfloat16* wsrc[2] = {w0 + (long long)e * expert_stride,
+                                  DUAL ? w1 + (long long)e * expert_stride : nullptr};
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int steps = (k + TK - 1) / TK;
+
+  auto fill = [&](int step) {
+    const int stage = step % kStages, k0 = step * TK;
+    // rows: TM x 4 pieces of 8 elements; weights: TN x 4 pieces a matrix
+    {
+      const int r = threadIdx.x >> 2, c = (threadIdx.x & 3) * 8;
+      const bool real = row0 + r < row_end && k0 + c < k;
+      copy16(&as[stage][r][c], real ? a + (long long)(row0 + r) * k + k0 + c : a, real);
+    }
+#pragma unroll
+    for (int m = 0; m < kW; ++m)
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int idx = threadIdx.x + i * 128;
+        const int r = idx >> 2, c = (idx & 3) * 8;
+        const bool real = n0 + r < n && k0 + c < k;
+        copy16(&ws[stage][m][r][c], real ? wsrc[m] + (long long)(n0 + r) * k + k0 + c : wsrc[m],
+               real);
+      }
+  };
+
+  float acc[kW][2][2][4] = {};           // [matrix][row tile of 16][column tile of 8][fragment]
+  for (int s = 0; s < kStages - 1; ++s) {
+    if (s < steps) fill(s);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  for (int step = 0; step < steps; ++step) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(kStages - 2) : "memory");
+    __syncthreads();
+    if (step + kStages - 1 < steps) fill(step + kStages - 1);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const int stage = step % kStages;
+#pragma unroll
+    for (int kk = 0; kk < TK; kk += 16) {
+      uint32_t af[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(
+            &as[stage][mt * 16 + (lane & 15)][kk + (lane >> 4) * 8]));
+        mma::ldmatrix_x4(addr, af[mt][0], af[mt][1], af[mt][2], af[mt][3]);
+      }
+#pragma unroll
+      for (int m = 0; m < kW; ++m) {
+        uint32_t bf[4];                  // (b0, b1) of column tile 0, then of column tile 1
+        const int nrow = warp * 16 + (lane >> 4) * 8 + (lane & 7);
+        const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(
+            &ws[stage][m][nrow][kk + ((lane >> 3) & 1) * 8]));
+        mma::ldmatrix_x4(addr, bf[0], bf[1], bf[2], bf[3]);
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          mma::bf16_16816(acc[m][mt][0], af[mt], bf[0], bf[1]);
+          mma::bf16_16816(acc[m][mt][1], af[mt], bf[2], bf[3]);
+        }
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int f = 0; f < 4; ++f) {
+        const int row = row0 + mt * 16 + (lane >> 2) + (f >> 1) * 8;
+        const int col = n0 + warp * 16 + nt * 8 + (lane & 3) * 2 + (f & 1);
+        if (row >= row_end || col >= n) continue;
+        if constexpr (DUAL) {
+          const float g = fminf(acc[0][mt][nt][f], limit);
+          const float u = fminf(fmaxf(acc[1][mt][nt][f], -limit), limit);
+          static_cast<__nv_bfloat16*>(out_v)[(long long)row * n + col] =
+              __float2bfloat16_rn(g / (1.f + expf(-alpha * g)) * (u + 1.f));
+        } else {
+          static_cast<float*>(out_v)[(long long)row * n + col] = acc[0][mt][nt][f];
+        }
+      }
+}
+
 // The dense form of the same activation for the shared expert: gate_up [T, 2 ff] -> [T, ff].
 template <typename T>
 __global__ void clamped_act_kernel(const T* __restrict__ gate_up, T* __restrict__ out,
@@ -232,6 +360,25 @@ SAKV_EXPORT int sakv_moe_route(const float* logits, long long ld, int experts, i
   return launch_ordered(route_kernel, dim3((unsigned)blocks), dim3(threads), 0, stream, logits, ld, experts, top, chosen, weights, counts, rank, tokens);
 }
 
+// out[t, o] = sum_i h[t, i] w[o, i] in fp32: h [tokens, width] of `dtype`, w fp32 [outputs,
+// width], out fp32 [tokens, outputs].
+SAKV_EXPORT int sakv_moe_logits(const void* h, int dtype, const float* w, float* out, int tokens,
+                                int outputs, int width, cudaStream_t stream) {
+  if (tokens < 0 || outputs <= 0 || width <= 0) return cudaErrorInvalidValue;
+  if (tokens == 0) return 0;
+  const long long count = (long long)tokens * outputs;
+  const long long blocks = (count * 32 + 255) / 256;
+  if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
+  const dim3 grid((unsigned)blocks), block(256);
+  if (dtype == SAKV_F32)
+    return launch_ordered(logits_kernel<float>, grid, block, 0, stream, (const float*)h, w, out,
+                          outputs, width, count);
+  if (dtype == SAKV_BF16)
+    return launch_ordered(logits_kernel<__nv_bfloat16>, grid, block, 0, stream,
+                          (const __nv_bfloat16*)h, w, out, outputs, width, count);
+  return cudaErrorInvalidValue;
+}
+
 SAKV_EXPORT int sakv_moe_plan(int32_t* counts, int32_t* offsets, int32_t* tile_expert,
                               int32_t* tile_row, int32_t* n_tiles, int experts, int max_tiles,
                               cudaStream_t stream) {
@@ -276,6 +423,20 @@ SAKV_EXPORT int sakv_moe_product(const void* a, int dtype, const void* w0, const
     SAKV_GROUPED(float, false);
   }
   if (dtype == SAKV_BF16) {
+    // the tensor-core tile wants 16-byte pieces: k a multiple of 8, aligned operands
+    if (k % 8 == 0 && !(((uintptr_t)a | (uintptr_t)w0 | (uintptr_t)w1) & 15) &&
+        expert_stride % 8 == 0) {
+      const dim3 threads(128);
+      if (dual)
+        return launch_ordered(grouped_tc_kernel<true>, grid, threads, 0, stream,
+                              (const __nv_bfloat16*)a, (const __nv_bfloat16*)w0,
+                              (const __nv_bfloat16*)w1, expert_stride, tile_expert, tile_row,
+                              offsets, n_tiles, out, n, k, limit, alpha);
+      return launch_ordered(grouped_tc_kernel<false>, grid, threads, 0, stream,
+                            (const __nv_bfloat16*)a, (const __nv_bfloat16*)w0,
+                            (const __nv_bfloat16*)w1, expert_stride, tile_expert, tile_row,
+                            offsets, n_tiles, out, n, k, limit, alpha);
+    }
     if (dual) SAKV_GROUPED(__nv_bfloat16, true);
     SAKV_GROUPED(__nv_bfloat16, false);
   }

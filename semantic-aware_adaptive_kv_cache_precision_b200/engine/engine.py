@@ -89,6 +89,8 @@ class Engine:
         """Check the checkpoint against the configuration, then put every tensor on
         the device; a model is never half loaded. If the device has no room the call
         raises `OutOfDeviceMemory` and the engine stays as it was before the call."""
+        from ..csrc import build as _build
+        _build.build_many(self.model.kernel_libraries())
         with torch.cuda.device(self.device):
             if self.model_dir is not None:
                 self.model.load(self.model_dir)

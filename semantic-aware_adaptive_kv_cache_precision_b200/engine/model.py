@@ -73,6 +73,13 @@ class DecoderModel:
         self.final_norm.bind(arena)
         self.arena = arena
 
+    def kernel_libraries(self) -> list:
+        """The kernel libraries this model's steps launch, as far as its parts name them."""
+        names = ["elementwise", "sampling"]
+        for block in list(self.blocks) + [self.final_norm]:
+            names += list(getattr(block, "kernel_libraries", ()))
+        return list(dict.fromkeys(names))
+
     @property
     def weight_bytes(self) -> int:
         return 0 if self.arena is None else self.arena.nbytes

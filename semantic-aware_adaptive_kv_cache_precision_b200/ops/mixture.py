@@ -29,6 +29,19 @@ def tile_rows() -> int:
     return plain_function("sakv_moe_tile_rows")()
 
 
+def router_logits(h: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """fp32 [T, outputs] = h weight^T with fp32 `weight` [outputs, width] and fp32 sums, h
+    [T, width] in either type: the router's product, 32-bit in both modes."""
+    require_cuda(h, weight)
+    _check(h.dim() == 2 and h.is_contiguous() and weight.dtype == torch.float32
+           and weight.is_contiguous() and weight.dim() == 2 and weight.shape[1] == h.shape[1],
+           "h: contiguous [T, width]; weight: fp32 [outputs, width]")
+    out = torch.empty((h.shape[0], weight.shape[0]), dtype=torch.float32, device=h.device)
+    call("sakv_moe_logits", ptr(h), dtype_code(h.dtype), ptr(weight), ptr(out), h.shape[0],
+         weight.shape[0], h.shape[1])
+    return out
+
+
 def route(logits: torch.Tensor, experts: int, top: int) -> Routing:
     """logits: fp32 [T, >= experts]; the `top` largest of the first `experts` columns a row."""
     require_cuda(logits)

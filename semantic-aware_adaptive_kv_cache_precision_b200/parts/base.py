@@ -62,6 +62,11 @@ class Part:
     #: decode steps kernel by kernel; it also falls back by itself if a capture fails.
     graph_safe = True
 
+    #: names of the kernel libraries (`csrc.build.LIBRARIES`) this part's step launches, as
+    #: far as the part knows them: the engine compiles a model's missing ones side by side
+    #: before the first step instead of one after the other at their first use
+    kernel_libraries: tuple = ()
+
     def __init__(self, spec, prefix: str, mode: str):
         self.spec, self.prefix, self.mode = spec, prefix, mode
         self.act_dtype = torch.float32 if mode == "float32" else torch.bfloat16

@@ -28,6 +28,8 @@ MAPS = 2
 
 
 class DifferentialAttention(Part):
+    kernel_libraries = ("attention_distance", "gemm_f32", "gemm_tc")
+
     def __init__(self, spec, prefix, mode):
         super().__init__(spec, prefix, mode)
         s = spec
@@ -75,25 +77,26 @@ class DifferentialAttention(Part):
         if write_cache:
             ops.kv_store(fused, self.q_cols, self.q_cols + self.k_cols, step.positions,
                          step.token_seq, view.block_table, view.keys, view.values)
+        splits, across = self._splits(step, fused)
         queries = fused[:, :self.q_cols].view(fused.shape[0], s.heads * MAPS, s.head_dim)
         gated = ops.cached_attention(
             queries, view.keys, view.values, step.positions, step.token_seq, view.block_table,
             s.heads, s.head_dim, s.value_dim, s.scale, maps=MAPS, chunk=s.chunk, lam=self.lam,
             out_scale=1.0 - s.diff, eps=s.eps,
             gate_elem_off=self.q_cols + self.k_cols + self.v_cols if s.gate else None,
-            splits=self._splits(step, fused))
+            splits=splits, key_splits=across)
         return ops.linear(gated, self.w_o, out_dtype=torch.float32)
 
-    def _splits(self, step, fused) -> int:
+    def _splits(self, step, fused) -> tuple:
+        """(warps, blocks) that share a token's keys; see `LatentAttention._splits`. A token
+        sees at most its chunk."""
         if fused.dtype == torch.float32 or not step.is_decode:
-            return 1
+            return 1, 1
+        s = self.spec
         keys = step.max_len_bound or step.max_len
-        if self.spec.chunk:
-            keys = min(keys, self.spec.chunk)
-        splits = 1
-        while splits < 16 and splits * 64 < keys:
-            splits *= 2
-        return splits
+        if s.chunk:
+            keys = min(keys, s.chunk)
+        return ops.plan_key_splits(keys, step.tokens * s.kv_heads, s.value_dim > 256)
 
     def forward(self, h, step, view, residual, write_cache=True):
         ops.add_into(residual, self.produce(h, step, view, write_cache))

@@ -24,6 +24,8 @@ from .base import Part, build_part, register_part
 
 
 class LatentAttention(Part):
+    kernel_libraries = ("latent", "attention_distance", "gemm_f32", "gemm_tc")
+
     def __init__(self, spec, prefix, mode):
         super().__init__(spec, prefix, mode)
         s = spec
@@ -94,30 +96,30 @@ class LatentAttention(Part):
         ops.rotate_heads(q, self.q_width, s.head_dim, s.heads, s.rot_dim, step.positions,
                          pos.cos, pos.sin)
         q3 = q.view(tokens, s.heads, self.q_width)
+        splits, across = self._splits(step, q)
         # every head's plain query in the latent's space
         in_latent = torch.empty((tokens, s.heads, rank), dtype=q.dtype, device=q.device)
         ops.per_head(q3[:, :, :s.head_dim], self.w_uk_t, in_latent)
         mixed = ops.cached_attention(
             in_latent, view.keys, None, step.positions, step.token_seq, view.block_table,
             s.heads, rank + s.rot_dim, rank, s.scale, q2=q3[:, :, s.head_dim:], q_split=rank,
-            splits=self._splits(step, q))
+            splits=splits, key_splits=across)
         # the weighted sums of latents to each head's values
         heads_out = torch.empty((tokens, s.heads, s.value_dim), dtype=q.dtype, device=q.device)
         ops.per_head(mixed.view(tokens, s.heads, rank), self.w_uv, heads_out)
         return ops.linear(heads_out.view(tokens, s.heads * s.value_dim), self.w_o,
                           out_dtype=torch.float32)
 
-    def _splits(self, step, q) -> int:
-        """How many warps share a token's keys: one in the 32-bit mode and for prompts (the
-        sums then have one order however the tokens are cut); for decode steps in bfloat16
-        one warp for every two chunks of 32 keys that a token can see, up to 16."""
+    def _splits(self, step, q) -> tuple:
+        """(warps, blocks) that share a token's keys: one each in the 32-bit mode and for
+        prompts (the sums then have one order however the tokens are cut); for decode steps in
+        bfloat16 what `ops.plan_key_splits` gives for the longest sequence the step's block
+        lists can hold (a captured step keeps its launch numbers as long as they do)."""
         if q.dtype == torch.float32 or not step.is_decode:
-            return 1
-        keys = step.max_len_bound or step.max_len
-        splits = 1
-        while splits < 16 and splits * 64 < keys:
-            splits *= 2
-        return splits
+            return 1, 1
+        s = self.spec
+        return ops.plan_key_splits(step.max_len_bound or step.max_len,
+                                   step.tokens * max(1, s.heads // 2), s.kv_rank > 256)
 
     def forward(self, h, step, view, residual, write_cache=True):
         ops.add_into(residual, self.produce(h, step, view, write_cache))

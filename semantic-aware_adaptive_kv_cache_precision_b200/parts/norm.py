@@ -35,6 +35,8 @@ class RMSNorm(Part):
 
 
 class LayerNorm(RMSNorm):
+    kernel_libraries = ("layer_norm", "elementwise")
+
     """`(x - mean) / sqrt(variance + eps) * w` over rows of the fp32 stream, no bias; the
     variance is the mean of the squared deviations (`csrc/layer_norm.cu`).
 

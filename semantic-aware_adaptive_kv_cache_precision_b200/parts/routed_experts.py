@@ -25,6 +25,8 @@ from .base import Part, register_part
 
 
 class RoutedExperts(Part):
+    kernel_libraries = ("moe", "gemm_f32", "gemm_tc")
+
     def __init__(self, spec, prefix, mode):
         super().__init__(spec, prefix, mode)
         if spec.score != "sigmoid":
@@ -81,8 +83,7 @@ class RoutedExperts(Part):
     def produce(self, h, step):
         """The feed-forward's output, fp32 [T, hidden]."""
         s = self.spec
-        logits = ops.linear(h if h.dtype == torch.float32 else h.float(), self.w_route,
-                            out_dtype=torch.float32)
+        logits = mixture.router_logits(h, self.w_route)
         routing = mixture.route(logits, s.experts, s.top)
         # (a checkpoint stored in 32 bits keeps its matrices so: the experts then run in 32 bits)
         rows = mixture.gather_rows(h if h.dtype == self.w_gate.dtype else h.to(self.w_gate.dtype),

@@ -68,6 +68,8 @@ class SandwichBlock(Part):
         self.parts = tuple(x for x in (self.mixer_norm, self.mixer_after, self.mixer,
                                        self.ffn_norm, self.ffn_after, self.ffn) if x is not None)
         self.graph_safe = all(getattr(part, "graph_safe", True) for part in self.parts)
+        self.kernel_libraries = tuple(n for part in self.parts
+                                      for n in getattr(part, "kernel_libraries", ()))
 
     def tensor_decls(self):
         return [d for part in self.parts for d in part.tensor_decls()]

@@ -145,15 +145,24 @@ def test_latent_attention_finds_a_key_far_back(dtype, heads, rank, rot):
     wide = torch.zeros((n, heads, 5 + rot), dtype=T, device=DEV)
     wide[:, :, 5:] = dev(qb, T)
     table = cache.table([0], n)
-    for lo, hi, splits in ((0, n, 1), (600, n, 1), (asker, asker + 1, 1), (asker, asker + 1, 4),
-                           (asker, asker + 1, 16), (0, 3, 1), (0, 1, 2)):
+    for lo, hi, splits, across in ((0, n, 1, 1), (600, n, 1, 1), (asker, asker + 1, 1, 1),
+                                   (asker, asker + 1, 4, 1), (asker, asker + 1, 16, 1), (0, 3, 1, 1),
+                                   (0, 1, 2, 1), (asker, asker + 2, 4, 4), (asker - 1, asker + 1, 8, 16),
+                                   (2, 4, 2, 8)):
         if dtype == "float32" and splits > 1:
             continue
         step = step_for([0] * (hi - lo), range(lo, hi))
         got = ops.cached_attention(dev(qa[lo:hi], T), cache.keys, None, step.positions,
                                    step.token_seq, table, heads, width, rank, scale,
-                                   q2=wide[lo:hi, :, 5:], q_split=rank, splits=splits)
-        close(got, want[lo:hi], T, f"positions {lo}..{hi}, {splits} warps")
+                                   q2=wide[lo:hi, :, 5:], q_split=rank, splits=splits,
+                                   key_splits=across, warp_stage=splits in (4, 8))
+        close(got, want[lo:hi], T, f"positions {lo}..{hi}, {splits} warps, {across} blocks")
+        if across > 1:      # the tickets were left clean: the same again
+            again = ops.cached_attention(dev(qa[lo:hi], T), cache.keys, None, step.positions,
+                                         step.token_seq, table, heads, width, rank, scale,
+                                         q2=wide[lo:hi, :, 5:], q_split=rank, splits=splits,
+                                         key_splits=across)
+            assert torch.equal(again, got)
 
 
 # -- two maps a head inside chunks ------------------------------------------------------------
@@ -200,9 +209,11 @@ def test_two_maps_inside_chunks_at_their_edges(dtype, heads, kv_heads, dim, vdim
     table = cache.table([0], n)
     q_cols = heads * 2 * dim
     fused = dev(np.concatenate([q.reshape(n, q_cols), np.zeros((n, 3)), gate], axis=1), T)
-    for lo, hi, splits in ((0, n, 1), (edge - 2 if edge else 0, edge + 3, 1), (edge, edge + 1, 1),
-                           (edge + 1, edge + 2, 2), (min(edge + size, n) - 1, min(edge + size, n), 8),
-                           (0, 2, 1), (130, 200, 1)):
+    last = min(edge + size, n)
+    for lo, hi, splits, across in ((0, n, 1, 1), (edge - 2 if edge else 0, edge + 3, 1, 1),
+                                   (edge, edge + 1, 1, 1), (edge + 1, edge + 2, 2, 1),
+                                   (last - 1, last, 8, 1), (0, 2, 1, 1), (130, 200, 1, 1),
+                                   (last - 2, last, 2, 4), (edge, edge + 2, 4, 2)):
         if dtype == "float32" and splits > 1:
             continue
         step = step_for([0] * (hi - lo), range(lo, hi))
@@ -210,8 +221,9 @@ def test_two_maps_inside_chunks_at_their_edges(dtype, heads, kv_heads, dim, vdim
         got = ops.cached_attention(part[:, :q_cols].view(hi - lo, heads * 2, dim), cache.keys,
                                    cache.values, step.positions, step.token_seq, table, heads, dim,
                                    vdim, scale, maps=2, chunk=chunk, lam=lam, out_scale=1 - diff,
-                                   eps=eps, gate_elem_off=q_cols + 3, splits=splits)
-        close(got, want[lo:hi], T, f"positions {lo}..{hi}, {splits} warps")
+                                   eps=eps, gate_elem_off=q_cols + 3, splits=splits,
+                                   key_splits=across, warp_stage=splits in (2, 8))
+        close(got, want[lo:hi], T, f"positions {lo}..{hi}, {splits} warps, {across} blocks")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -302,7 +314,7 @@ def plain_mixture(h, t, experts, top, limit, weight_input=True):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("n,width,experts,top,ff", [
     (1, 64, 2, 1, 96), (77, 96, 6, 2, 48), (5, 100, 3, 3, 50), (200, 64, 40, 4, 24),
-    (33, 72, 7, 1, 130)])
+    (33, 72, 7, 1, 130), (300, 200, 5, 2, 72), (9, 36, 4, 2, 20)])
 def test_routed_experts_against_the_plain_mixture(dtype, n, width, experts, top, ff):
     T = TYPES[dtype]
     rng = np.random.default_rng(n + experts)
@@ -317,8 +329,10 @@ def test_routed_experts_against_the_plain_mixture(dtype, n, width, experts, top,
         t[f"e{e}.gate"] = rounded(rng.standard_normal((ff, width)) * 0.2, T)
         t[f"e{e}.up"] = rounded(rng.standard_normal((ff, width)) * 0.2, T)
         t[f"e{e}.down"] = rounded(rng.standard_normal((width, ff)) * 0.2, T)
-    logits = dev(h @ t["router"].T)
+    logits = mixture.router_logits(dev(h, T), dev(t["router"]))
     z = logits.cpu().numpy().astype(np.float64)
+    exact = h @ dev(t["router"]).cpu().numpy().astype(np.float64).T
+    assert np.abs(z - exact).max() <= 1e-5 * np.abs(exact).max()
     routing = mixture.route(logits, experts, top)
     chosen = np.argsort(-z, axis=-1, kind="stable")[:, :top]
     assert np.array_equal(routing.chosen.cpu().numpy(), chosen)

@@ -42,7 +42,7 @@ MIXED = {"architecture": "Venanex", "vocab": 211, "width": 96, "norm": {"eps": 1
                     latent(3, 24, 16, 16, 56, None, 0.16, 500.0, None, moe(5, 5, 40, 0.7)),
                     attention(2, 2, 32, 16, 0.18, 0.3, None, moe(3, 1, 64, 2.5, (80, 0.9)))]}
 PLAIN = {"architecture": "Venanex", "vocab": 150, "width": 64, "norm": {"eps": 1e-6},
-         "initializer_range": 0.15,
+         "initializer_range": 0.08,
          "layers": [attention(1, 1, 64, 64, 0.125, 0.4, 64, moe(2, 1, 96, 1.2, (16, 1.0))),
                     latent(1, 8, 32, 8, 16, 48, 0.3, 100.0, (2.0, 32, 16.0, 1.0), None)]}
 ODD = {"architecture": "Venanex", "vocab": 131, "width": 100, "norm": {"eps": 3e-6},
