@@ -50,6 +50,11 @@ struct AttentionExtra {
   long long scratch_floats;
   int* tickets;              // [items], zero on entry and on exit
   int warp_stage;            // decode: every warp copies its chunks into shared memory first
+  // Decoded tokens, one warp a group of heads: the items run over a token's groups of heads
+  // first, a block's warps are the groups of ONE token and key/value head, and they share every
+  // chunk of its keys through shared memory as a prompt's consecutive tokens do (the rows are
+  // read once for all of the token's heads); `key_splits` blocks take ranges of the chunks.
+  int heads_first;
 };
 
 namespace {
@@ -243,7 +248,20 @@ distance_attention_tiled_kernel(
   // (the same for every thread of the block)
   bool staged = false;
   int block_first = 0, block_last = 0;
-  if (stage_ok && splits == 1) {
+  const int groups = kv_heads * per_group;
+  int key_part = 0, key_parts = 1;       // this block's range of the chunks, when they are split
+  if (stage_ok == 1 && splits == 1 && x.heads_first) {
+    const long long item0 = (long long)blockIdx.x * warps, last = item0 + warps - 1;
+    if (last < items && item0 / groups == last / groups &&
+        (item0 % groups) / per_group == (last % groups) / per_group) {
+      staged = true;
+      const int p0 = positions[item0 / groups];
+      block_first = first_visible(p0, window, x.chunk);
+      block_last = p0;
+      key_part = x.key_splits > 1 ? (int)blockIdx.y : 0;
+      key_parts = x.key_splits > 1 ? x.key_splits : 1;
+    }
+  } else if (stage_ok == 1 && splits == 1) {
     const long long item0 = (long long)blockIdx.x * warps, last = item0 + warps - 1;
     if (last < items && item0 / tokens == last / tokens) {
       const int t0 = static_cast<int>(item0 % tokens), t1 = t0 + warps - 1;
@@ -256,8 +274,8 @@ distance_attention_tiled_kernel(
     }
   }
   if (active) {
-    t = static_cast<int>(item % tokens);
-    const int rest = static_cast<int>(item / tokens);
+    t = static_cast<int>(x.heads_first ? item / groups : item % tokens);
+    const int rest = static_cast<int>(x.heads_first ? item % groups : item / tokens);
     const int qi = rest % per_group;
     g = rest / per_group;
     h0 = g * hg + qi * P;
@@ -394,6 +412,7 @@ distance_attention_tiled_kernel(
       return ((long long)table[c >> 1] * kv_heads + g) * kCacheBlock + (c & 1) * 32;
     };
     if (!staged) {
+      // (with split keys, whatever the form: block y takes every key_splits-th turn)
       const int c0 = first / 32 + (x.key_splits > 1 ? (int)blockIdx.y * splits : 0) + split;
       for (int c = c0; c <= pos / 32; c += splits * (x.key_splits > 1 ? x.key_splits : 1)) {
         const long long rows = rows_of(c);
@@ -434,7 +453,12 @@ distance_attention_tiled_kernel(
       const int kstride = k_row + kPiece;            // padded: the lanes' rows hit different banks
       T* stage = reinterpret_cast<T*>(shared + (long long)warps * P * row_floats);
       const int per_buffer = 32 * (kstride + (x.v_in_k ? 0 : vdim));
-      const int c_lo = block_first / 32, c_hi = block_last / 32;
+      int c_lo = block_first / 32, c_hi = block_last / 32;
+      if (key_parts > 1) {               // a contiguous share of the chunks for this block
+        const int share = (c_hi - c_lo + key_parts) / key_parts;
+        c_lo += key_part * share;
+        c_hi = c_hi < c_lo + share - 1 ? c_hi : c_lo + share - 1;
+      }
       auto fetch = [&](int c, int buffer) {
         const long long rows = rows_of(c);
         T* ks = stage + buffer * per_buffer;
@@ -450,7 +474,7 @@ distance_attention_tiled_kernel(
         }
         copies_commit();
       };
-      fetch(c_lo, 0);
+      if (c_lo <= c_hi) fetch(c_lo, 0);
       int buffer = 0;
       for (int c = c_lo; c <= c_hi; ++c, buffer ^= 1) {
         if (c < c_hi) fetch(c + 1, buffer ^ 1);
@@ -504,51 +528,52 @@ distance_attention_tiled_kernel(
 #pragma unroll
       for (int i = 0; i < VPL; ++i) acc[p][i] = sum[i];
     }
-    if (x.key_splits > 1) {              // (uniform over the grid; this warp is the item's)
-      const int S = x.key_splits;
-      float* part = x.scratch + ((item * S + blockIdx.y) * P) * (long long)row_floats;
-#pragma unroll
-      for (int p = 0; p < P; ++p) {
-        float* row = part + (long long)p * row_floats;
-        if (lane == 0) {
-          row[0] = m[p];
-          row[1] = l[p];
-        }
-#pragma unroll
-        for (int i = 0; i < VPL; ++i)
-          if (lane * VPL + i < vdim) row[2 + lane * VPL + i] = acc[p][i];
-      }
-      __threadfence();
-      int ticket = 0;
-      if (lane == 0) ticket = atomicAdd(x.tickets + item, 1);
-      ticket = __shfl_sync(0xffffffffu, ticket, 0);
-      if (ticket != S - 1) return;
-      __threadfence();
-      if (lane == 0) x.tickets[item] = 0;
-      const float* all = x.scratch + (item * S * P) * (long long)row_floats;
-#pragma unroll
-      for (int p = 0; p < P; ++p) {
-        float top = -INFINITY;
-        for (int w = 0; w < S; ++w) top = fmaxf(top, __ldcg(all + ((long long)w * P + p) * row_floats));
-        float total = 0.f, sum[VPL];
-#pragma unroll
-        for (int i = 0; i < VPL; ++i) sum[i] = 0.f;
-        for (int w = 0; w < S; ++w) {
-          const float* row = all + ((long long)w * P + p) * row_floats;
-          const float mw = __ldcg(row);
-          const float f = mw == -INFINITY ? 0.f : expf(mw - top);
-          total = fmaf(__ldcg(row + 1), f, total);
-#pragma unroll
-          for (int i = 0; i < VPL; ++i)
-            if (lane * VPL + i < vdim) sum[i] = fmaf(__ldcg(row + 2 + lane * VPL + i), f, sum[i]);
-        }
-        l[p] = total;
-#pragma unroll
-        for (int i = 0; i < VPL; ++i) acc[p][i] = sum[i];
-      }
-    }
   }
   if (!active) return;
+  if (x.key_splits > 1) {              // (uniform over the grid; this warp is the item's)
+    const int S = x.key_splits;
+    float* part = x.scratch + ((item * S + blockIdx.y) * P) * (long long)row_floats;
+#pragma unroll
+    for (int p = 0; p < P; ++p) {
+      float* row = part + (long long)p * row_floats;
+      if (lane == 0) {
+        row[0] = m[p];
+        row[1] = l[p];
+      }
+#pragma unroll
+      for (int i = 0; i < VPL; ++i)
+        if (lane * VPL + i < vdim) row[2 + lane * VPL + i] = acc[p][i];
+    }
+    __threadfence();
+    int ticket = 0;
+    if (lane == 0) ticket = atomicAdd(x.tickets + item, 1);
+    ticket = __shfl_sync(0xffffffffu, ticket, 0);
+    if (ticket != S - 1) return;
+    __threadfence();
+    if (lane == 0) x.tickets[item] = 0;
+    const float* all = x.scratch + (item * S * P) * (long long)row_floats;
+#pragma unroll
+    for (int p = 0; p < P; ++p) {
+      float top = -INFINITY;
+      for (int w = 0; w < S; ++w) top = fmaxf(top, __ldcg(all + ((long long)w * P + p) * row_floats));
+      float total = 0.f, sum[VPL];
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) sum[i] = 0.f;
+#pragma unroll 4                    // (several splits' rows asked for before the first is used)
+      for (int w = 0; w < S; ++w) {
+        const float* row = all + ((long long)w * P + p) * row_floats;
+        const float mw = __ldcg(row);
+        const float f = mw == -INFINITY ? 0.f : expf(mw - top);
+        total = fmaf(__ldcg(row + 1), f, total);
+#pragma unroll
+        for (int i = 0; i < VPL; ++i)
+          if (lane * VPL + i < vdim) sum[i] = fmaf(__ldcg(row + 2 + lane * VPL + i), f, sum[i]);
+      }
+      l[p] = total;
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) acc[p][i] = sum[i];
+    }
+  }
   if constexpr (MAPS == 2) {
     // two maps a head over the same values: o = a1 - lambda a2, unit root mean square over
     // the head's values, the scale, and the gate element by element
@@ -615,6 +640,14 @@ int launch_tiled(const void* qkv, long long stride, int gate_off, void* out, con
   row_floats = (row_floats + 3) / 4 * 4;                     // rows stay 16-byte aligned
   int warps = splits > 1 ? splits : (tokens >= 64 ? 8 : 4);     // (a block's tokens share keys)
   if (VPL >= 16 && warps > 8) warps = 8;                        // (the kernel's launch bounds)
+  if (x.heads_first && splits == 1) {
+    // a block's warps are groups of heads of one token and key/value head: as many as divide
+    // the groups there are, so that no block lies across two tokens
+    const int cap = VPL >= 16 ? 8 : 16;
+    warps = 1;
+    for (int w = 1; w <= cap && w <= per_group; ++w)
+      if (per_group % w == 0) warps = w;
+  }
   while ((size_t)warps * P * row_floats * sizeof(float) > (size_t)kBudget && warps > 1) warps /= 2;
   if ((size_t)warps * P * row_floats * sizeof(float) > (size_t)kBudget) return cudaErrorInvalidValue;
   if (splits > 1) splits = warps;
@@ -625,8 +658,8 @@ int launch_tiled(const void* qkv, long long stride, int gate_off, void* out, con
   const bool copies_fit = (x.k_row * sizeof(T)) % 16 == 0 && (vdim * sizeof(T)) % 16 == 0 &&
                           (x.v_row * sizeof(T)) % 16 == 0 && !((uintptr_t)k_cache & 15) &&
                           !((uintptr_t)v_cache & 15);
-  int stage_ok = splits == 1 && warps >= 4 && tokens >= warps && copies_fit &&
-                 smem + staging <= (size_t)kBudget;
+  int stage_ok = splits == 1 && copies_fit && smem + staging <= (size_t)kBudget &&
+                 (x.heads_first || (warps >= 4 && tokens >= warps));
   if (stage_ok) smem += staging;
   // a decoded token's warps: a chunk's rows a warp (`stage_ok` 2), where the step asked for it
   if (splits > 1 && x.warp_stage && copies_fit &&
@@ -639,7 +672,8 @@ int launch_tiled(const void* qkv, long long stride, int gate_off, void* out, con
   if (blocks > 0x7fffffffLL) return cudaErrorInvalidValue;
   unsigned across = 1;
   if (x.key_splits > 1) {
-    if (splits <= 1 || x.key_splits > 64 || x.scratch == nullptr || x.tickets == nullptr ||
+    if ((splits <= 1 && !x.heads_first) || x.key_splits > 64 || x.scratch == nullptr ||
+        x.tickets == nullptr ||
         items * x.key_splits * P * row_floats > x.scratch_floats)
       return cudaErrorInvalidValue;
     across = (unsigned)x.key_splits;
@@ -677,7 +711,12 @@ int pick_tiled(const void* qkv, long long stride, int gate_off, void* out, const
   if (vdim <= 256) { SAKV_TILED_P(8); }
   // (sixteen columns a lane: two heads a warp at most, for the registers' sake)
   if (maps == 2) SAKV_TILED(2, 16, 2);
-  if (hg == 1) SAKV_TILED(1, 16, 1);
+  // (a decoded token's groups of heads share their rows through shared memory: one head a
+  // warp costs no reads and gives a block twice the warps, which pays while the step's tokens
+  // leave SMs idle: 8 tokens of 8 heads 598 against 714 us over six layers, 64 tokens 417
+  // against 304 us a layer)
+  if (hg == 1 || (x.heads_first && (long long)tokens * heads <= 2LL * sm_count()))
+    SAKV_TILED(1, 16, 1);
   SAKV_TILED(2, 16, 1);
 #undef SAKV_TILED_P
 #undef SAKV_TILED
@@ -784,6 +823,9 @@ SAKV_EXPORT int sakv_distance_attention(const void* qkv, int dtype, long long st
 // keys as well; `scratch` (floats, at least tokens * kv_heads * (heads * maps / kv_heads + 3) *
 // key_splits * (max(dim, vdim + 2) + 4)) holds their sums and `tickets` (int32 for every
 // token, kv head and group of heads; zero on entry, left zero) tells which block came last.
+// `heads_first` (with splits 1): the form for decoded tokens in which a block's warps are one
+// token's groups of heads and share each chunk of keys through shared memory; `key_splits`
+// blocks then take contiguous shares of the chunks.
 SAKV_EXPORT int sakv_cached_attention(
     const void* qkv, int dtype, long long stride, int q_head_stride, const void* q2,
     long long q2_stride, int q2_head_stride, int q_split, int gate_off, void* out,
@@ -792,7 +834,7 @@ SAKV_EXPORT int sakv_cached_attention(
     int max_blocks, int tokens, int heads, int kv_heads, int maps, int dim, int vdim, float scale,
     int window, int chunk, float lambda, float out_scale, float eps, int gate_elem_off,
     int splits, int key_splits, float* scratch, long long scratch_floats, int* tickets,
-    int warp_stage, cudaStream_t stream) {
+    int warp_stage, int heads_first, cudaStream_t stream) {
   if (tokens < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads || dim <= 0 || vdim <= 0 ||
       dim > 640 || vdim > 512 || max_blocks <= 0 || window < 0 || chunk < 0 ||
       (window > 0 && chunk > 0) || splits < 1 || splits > 16 || (maps != 1 && maps != 2) ||
@@ -821,6 +863,7 @@ SAKV_EXPORT int sakv_cached_attention(
   x.scratch_floats = scratch_floats;
   x.tickets = tickets;
   x.warp_stage = warp_stage;
+  x.heads_first = heads_first && splits == 1;
   const void* values = x.v_in_k ? k_cache : v_cache;
   if (dtype == SAKV_F32)
     return pick_tiled<float>(qkv, stride, gate_off, out, k_cache, values, positions, token_seq,

@@ -20,13 +20,13 @@ from . import mixture
 from .mixture import latent_prepare, rotate_heads
 from .attention import (attention_decode, attention_prefill, attention_prefill_tc, decode_splits,
                         forget_descriptors,
-                        fast_path_takes, kernel_errors, plan_key_splits, plan_wide_tiles, tc_prefill_takes, upload_query_tiles,
+                        fast_path_takes, kernel_errors, plan_key_splits, plan_token_blocks, plan_wide_tiles, tc_prefill_takes, upload_query_tiles,
                         upload_wide_plan)
 
 __all__ = ["CACHE_BLOCK", "KernelError", "embed", "rms_norm", "rope_store", "attention_plain",
            "attention_decode", "attention_prefill", "attention_prefill_tc", "tc_prefill_takes", "plan_wide_tiles", "upload_wide_plan",
            "upload_query_tiles",
-           "decode_splits", "plan_key_splits", "fast_path_takes", "forget_descriptors",
+           "decode_splits", "plan_key_splits", "plan_token_blocks", "fast_path_takes", "forget_descriptors",
            "kernel_errors", "gated_silu", "gelu_tanh", "streams_step", "streams_spread", "token_shift",
            "delta_rule", "kv_store", "layer_norm", "cached_attention", "mixture", "latent_prepare",
            "rotate_heads", "distance_attention", "gated_up", "gemm_tc", "add_into", "scale_cap_", "linear", "per_head", "choose", "Deferred"]
@@ -252,7 +252,8 @@ def cached_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      q2: torch.Tensor | None = None, q_split: int = 0,
                      window: int | None = None, chunk: int | None = None, lam: float = 0.0,
                      out_scale: float = 1.0, eps: float = 0.0, gate_elem_off: int | None = None,
-                     splits: int = 1, key_splits: int = 1, warp_stage: bool = False) -> torch.Tensor:
+                     splits: int = 1, key_splits: int = 1, warp_stage: bool = False,
+                     heads_first: bool = False) -> torch.Tensor:
     """Causal attention of every token of the step over its sequence's cache, in the general
     form of `csrc/attention_distance.cu`: scores, softmax weights and weighted sums in fp32.
 
@@ -270,7 +271,10 @@ def cached_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     many blocks of such warps do (long sequences, few tokens), folding through device memory;
     `warp_stage`: each of those warps first copies a chunk's rows into shared memory, all
     copies in flight at once (where the rows' sizes allow 16-byte copies and the block's
-    shared memory holds them)."""
+    shared memory holds them). `heads_first` (with `splits` 1; decode steps): a block's warps
+    are ONE token's groups of heads and share every chunk of its keys through shared memory, so
+    the rows are read once for all the token's heads; `key_splits` blocks a token then take
+    contiguous shares of the chunks."""
     require_cuda(q, k_cache, v_cache, positions, token_seq, block_table, q2)
     tokens = q.shape[0]
     _check(q.dim() == 3 and q.stride(2) == 1 and q.shape[1] == heads * maps
@@ -296,7 +300,8 @@ def cached_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     out = torch.empty((tokens, heads * vdim), dtype=q.dtype, device=q.device)
     scratch = tickets = None
     floats = 0
-    if key_splits > 1 and splits > 1:
+    heads_first = bool(heads_first) and splits == 1
+    if key_splits > 1 and (splits > 1 or heads_first):
         groups = tokens * kv_heads * (heads * maps // kv_heads + 3)
         floats = groups * key_splits * (max(dim, vdim + 2) + 4)
         scratch = torch.empty(floats, dtype=torch.float32, device=q.device)
@@ -313,7 +318,8 @@ def cached_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
          ptr(block_table), block_table.shape[1], tokens, heads, kv_heads, maps, dim, vdim,
          float(scale), int(window) if window else 0, int(chunk) if chunk else 0, float(lam),
          float(out_scale), float(eps), -1 if gate_elem_off is None else int(gate_elem_off),
-         int(splits), int(key_splits), ptr(scratch), floats, ptr(tickets), int(warp_stage))
+         int(splits), int(key_splits), ptr(scratch), floats, ptr(tickets), int(warp_stage),
+         int(heads_first))
     return out
 
 

@@ -37,7 +37,7 @@ SIGNATURES = {
                                 [P, I, L, I, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, P, I, P]),
     "sakv_cached_attention": ("attention_distance",
                               [P, I, L, I, P, L, I, I, I, P, P, I, P, I, P, P, P, I, I, I, I, I, I,
-                               I, F, I, I, F, F, F, I, I, I, P, L, P, I, P]),
+                               I, F, I, I, F, F, F, I, I, I, P, L, P, I, I, P]),
     "sakv_layer_norm": ("layer_norm", [P, P, P, P, P, I, P, I, I, I, F, P]),
     "sakv_latent_prepare": ("latent", [P, L, I, I, I, P, P, I, F, P, P, P, I, P, P, P, P, I, I, I,
                                        P]),

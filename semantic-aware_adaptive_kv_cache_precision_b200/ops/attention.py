@@ -323,3 +323,15 @@ def plan_key_splits(keys: int, items: int, wide: bool) -> tuple:
     while across < 16 and chunks > 2 * splits * across and 2 * items * across <= 8 * sm_count():
         across *= 2
     return splits, (across if splits > 1 else 1)
+
+
+def plan_token_blocks(keys: int, token_groups: int) -> int:
+    """Blocks that share the chunks of one decoded token's keys in
+    `ops.cached_attention(..., heads_first=True)`: one for every four chunks of 32 keys, up
+    to 16, fewer while the grid would pass four blocks an SM. `keys`: the most keys a token can
+    see; `token_groups`: tokens x key/value heads."""
+    chunks = max(1, -(-int(keys) // 32))
+    across = 1
+    while across < 16 and chunks > 4 * across and token_groups * across * 2 <= 4 * sm_count():
+        across *= 2
+    return across

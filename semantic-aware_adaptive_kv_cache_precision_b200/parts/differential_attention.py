@@ -77,26 +77,25 @@ class DifferentialAttention(Part):
         if write_cache:
             ops.kv_store(fused, self.q_cols, self.q_cols + self.k_cols, step.positions,
                          step.token_seq, view.block_table, view.keys, view.values)
-        splits, across = self._splits(step, fused)
         queries = fused[:, :self.q_cols].view(fused.shape[0], s.heads * MAPS, s.head_dim)
         gated = ops.cached_attention(
             queries, view.keys, view.values, step.positions, step.token_seq, view.block_table,
             s.heads, s.head_dim, s.value_dim, s.scale, maps=MAPS, chunk=s.chunk, lam=self.lam,
             out_scale=1.0 - s.diff, eps=s.eps,
             gate_elem_off=self.q_cols + self.k_cols + self.v_cols if s.gate else None,
-            splits=splits, key_splits=across)
+            **self._decode_form(step, fused))
         return ops.linear(gated, self.w_o, out_dtype=torch.float32)
 
-    def _splits(self, step, fused) -> tuple:
-        """(warps, blocks) that share a token's keys; see `LatentAttention._splits`. A token
-        sees at most its chunk."""
+    def _decode_form(self, step, fused) -> dict:
+        """See `LatentAttention._decode_form`; a token sees at most its chunk."""
         if fused.dtype == torch.float32 or not step.is_decode:
-            return 1, 1
+            return {}
         s = self.spec
         keys = step.max_len_bound or step.max_len
         if s.chunk:
             keys = min(keys, s.chunk)
-        return ops.plan_key_splits(keys, step.tokens * s.kv_heads, s.value_dim > 256)
+        return {"heads_first": True,
+                "key_splits": ops.plan_token_blocks(keys, step.tokens * s.kv_heads)}
 
     def forward(self, h, step, view, residual, write_cache=True):
         ops.add_into(residual, self.produce(h, step, view, write_cache))

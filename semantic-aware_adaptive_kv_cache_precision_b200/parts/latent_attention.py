@@ -96,30 +96,31 @@ class LatentAttention(Part):
         ops.rotate_heads(q, self.q_width, s.head_dim, s.heads, s.rot_dim, step.positions,
                          pos.cos, pos.sin)
         q3 = q.view(tokens, s.heads, self.q_width)
-        splits, across = self._splits(step, q)
         # every head's plain query in the latent's space
         in_latent = torch.empty((tokens, s.heads, rank), dtype=q.dtype, device=q.device)
         ops.per_head(q3[:, :, :s.head_dim], self.w_uk_t, in_latent)
         mixed = ops.cached_attention(
             in_latent, view.keys, None, step.positions, step.token_seq, view.block_table,
             s.heads, rank + s.rot_dim, rank, s.scale, q2=q3[:, :, s.head_dim:], q_split=rank,
-            splits=splits, key_splits=across)
+            **self._decode_form(step, q))
         # the weighted sums of latents to each head's values
         heads_out = torch.empty((tokens, s.heads, s.value_dim), dtype=q.dtype, device=q.device)
         ops.per_head(mixed.view(tokens, s.heads, rank), self.w_uv, heads_out)
         return ops.linear(heads_out.view(tokens, s.heads * s.value_dim), self.w_o,
                           out_dtype=torch.float32)
 
-    def _splits(self, step, q) -> tuple:
-        """(warps, blocks) that share a token's keys: one each in the 32-bit mode and for
-        prompts (the sums then have one order however the tokens are cut); for decode steps in
-        bfloat16 what `ops.plan_key_splits` gives for the longest sequence the step's block
-        lists can hold (a captured step keeps its launch numbers as long as they do)."""
+    def _decode_form(self, step, q) -> dict:
+        """How a step's tokens share their keys. Prompts, and everything in the 32-bit mode:
+        a warp a token and group of heads walks the keys alone (the sums then have one order
+        however the tokens are cut). Decode steps in bfloat16: a block's warps are one token's
+        groups of heads and share each chunk of rows through shared memory, and several blocks
+        a token take shares of the chunks, as many as `ops.plan_token_blocks` gives for the
+        longest sequence the step's block lists can hold (a captured step keeps its launch
+        numbers as long as they do)."""
         if q.dtype == torch.float32 or not step.is_decode:
-            return 1, 1
-        s = self.spec
-        return ops.plan_key_splits(step.max_len_bound or step.max_len,
-                                   step.tokens * max(1, s.heads // 2), s.kv_rank > 256)
+            return {}
+        return {"heads_first": True,
+                "key_splits": ops.plan_token_blocks(step.max_len_bound or step.max_len, step.tokens)}
 
     def forward(self, h, step, view, residual, write_cache=True):
         ops.add_into(residual, self.produce(h, step, view, write_cache))

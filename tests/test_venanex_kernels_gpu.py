@@ -148,20 +148,24 @@ def test_latent_attention_finds_a_key_far_back(dtype, heads, rank, rot):
     for lo, hi, splits, across in ((0, n, 1, 1), (600, n, 1, 1), (asker, asker + 1, 1, 1),
                                    (asker, asker + 1, 4, 1), (asker, asker + 1, 16, 1), (0, 3, 1, 1),
                                    (0, 1, 2, 1), (asker, asker + 2, 4, 4), (asker - 1, asker + 1, 8, 16),
-                                   (2, 4, 2, 8)):
+                                   (2, 4, 2, 8), (asker, asker + 1, 1, -1), (asker - 1, asker + 2, 1, -4),
+                                   (asker, asker + 1, 1, -16), (0, 2, 1, -2), (40, 41, 1, -8)):
         if dtype == "float32" and splits > 1:
             continue
+        first = across < 0                      # (negative: the heads-first form)
+        across = abs(across)
         step = step_for([0] * (hi - lo), range(lo, hi))
         got = ops.cached_attention(dev(qa[lo:hi], T), cache.keys, None, step.positions,
                                    step.token_seq, table, heads, width, rank, scale,
                                    q2=wide[lo:hi, :, 5:], q_split=rank, splits=splits,
-                                   key_splits=across, warp_stage=splits in (4, 8))
+                                   key_splits=across, warp_stage=splits in (4, 8),
+                                   heads_first=first)
         close(got, want[lo:hi], T, f"positions {lo}..{hi}, {splits} warps, {across} blocks")
         if across > 1:      # the tickets were left clean: the same again
             again = ops.cached_attention(dev(qa[lo:hi], T), cache.keys, None, step.positions,
                                          step.token_seq, table, heads, width, rank, scale,
                                          q2=wide[lo:hi, :, 5:], q_split=rank, splits=splits,
-                                         key_splits=across)
+                                         key_splits=across, heads_first=first)
             assert torch.equal(again, got)
 
 
@@ -213,16 +217,21 @@ def test_two_maps_inside_chunks_at_their_edges(dtype, heads, kv_heads, dim, vdim
     for lo, hi, splits, across in ((0, n, 1, 1), (edge - 2 if edge else 0, edge + 3, 1, 1),
                                    (edge, edge + 1, 1, 1), (edge + 1, edge + 2, 2, 1),
                                    (last - 1, last, 8, 1), (0, 2, 1, 1), (130, 200, 1, 1),
-                                   (last - 2, last, 2, 4), (edge, edge + 2, 4, 2)):
+                                   (last - 2, last, 2, 4), (edge, edge + 2, 4, 2),
+                                   (last - 1, last, 1, -1), (last - 2, last, 1, -4),
+                                   (edge, edge + 2, 1, -2), (edge + 1, edge + 2, 1, -8)):
         if dtype == "float32" and splits > 1:
             continue
+        first = across < 0                      # (negative: the heads-first form)
+        across = abs(across)
         step = step_for([0] * (hi - lo), range(lo, hi))
         part = fused[lo:hi]
         got = ops.cached_attention(part[:, :q_cols].view(hi - lo, heads * 2, dim), cache.keys,
                                    cache.values, step.positions, step.token_seq, table, heads, dim,
                                    vdim, scale, maps=2, chunk=chunk, lam=lam, out_scale=1 - diff,
                                    eps=eps, gate_elem_off=q_cols + 3, splits=splits,
-                                   key_splits=across, warp_stage=splits in (2, 8))
+                                   key_splits=across, warp_stage=splits in (2, 8),
+                                   heads_first=first)
         close(got, want[lo:hi], T, f"positions {lo}..{hi}, {splits} warps, {across} blocks")
 
 
@@ -248,6 +257,13 @@ def test_attention_over_two_sequences_of_one_step(dtype):
     got = ops.cached_attention(dev(q.reshape(4, heads * 2, dim), T), cache.keys, cache.values,
                                i32(pos), i32(seq), table, heads, dim, vdim, scale, maps=2,
                                chunk=64, lam=0.5, out_scale=1.0, eps=1e-6)
+    if dtype == "bfloat16":                      # one block and three blocks a token
+        for across in (1, 3):
+            other = ops.cached_attention(dev(q.reshape(4, heads * 2, dim), T), cache.keys,
+                                         cache.values, i32(pos), i32(seq), table, heads, dim, vdim,
+                                         scale, maps=2, chunk=64, lam=0.5, out_scale=1.0, eps=1e-6,
+                                         heads_first=True, key_splits=across)
+            assert float((other.float() - got.float()).abs().max()) <= 2e-2
     for i, (s, p) in enumerate(take):
         k, v, qq = data[s]
         visible = (np.arange(lens[s]) <= p) & (np.arange(lens[s]) // 64 == p // 64)
