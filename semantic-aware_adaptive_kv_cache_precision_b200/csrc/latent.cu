@@ -83,9 +83,10 @@ int prepare(const float* down, long long stride, int q_rank, int rank, int rot,
             const int32_t* token_seq, const int32_t* block_table, int max_blocks,
             const float* cos_t, const float* sin_t, void* q_latent, void* cache, int write_cache,
             int tokens, cudaStream_t stream) {
-  return launch_ordered(latent_prepare_kernel<W, T>, dim3(tokens), dim3(kThreads), 0, stream, down, stride, q_rank, rank, rot, (const W*)q_weight,
-                           (const W*)kv_weight, eps, positions, token_seq, block_table,
-                           max_blocks, cos_t, sin_t, (T*)q_latent, (T*)cache, write_cache);
+  return launch_ordered(latent_prepare_kernel<W, T>, dim3(tokens), dim3(kThreads), 0, stream, down,
+                        stride, q_rank, rank, rot, (const W*)q_weight, (const W*)kv_weight, eps,
+                        positions, token_seq, block_table, max_blocks, cos_t, sin_t,
+                        (T*)q_latent, (T*)cache, write_cache);
 }
 
 }  // namespace
@@ -129,11 +130,11 @@ SAKV_EXPORT int sakv_rotate_heads(void* x, int dtype, long long stride, int head
   const long long count = (long long)tokens * heads * (rot / 2);
   const dim3 grid(grid_for(count, 256)), block(256);
   if (dtype == SAKV_F32)
-    return launch_ordered(rotate_heads_kernel<float>, grid, block, 0, stream, (float*)x,
-                             stride, head_stride, offset, heads, rot, positions, cos_t, sin_t,
-                             count);
+    return launch_ordered(rotate_heads_kernel<float>, grid, block, 0, stream, (float*)x, stride,
+                          head_stride, offset, heads, rot, positions, cos_t, sin_t, count);
   if (dtype == SAKV_BF16)
-    return launch_ordered(rotate_heads_kernel<__nv_bfloat16>, grid, block, 0, stream, (__nv_bfloat16*)x, stride, head_stride, offset, heads, rot, positions,
-                             cos_t, sin_t, count);
+    return launch_ordered(rotate_heads_kernel<__nv_bfloat16>, grid, block, 0, stream,
+                          (__nv_bfloat16*)x, stride, head_stride, offset, heads, rot, positions,
+                          cos_t, sin_t, count);
   return cudaErrorInvalidValue;
 }

@@ -357,7 +357,8 @@ SAKV_EXPORT int sakv_moe_route(const float* logits, long long ld, int experts, i
   if (tokens == 0) return 0;
   const int threads = 128;
   const long long blocks = ((long long)tokens * 32 + threads - 1) / threads;
-  return launch_ordered(route_kernel, dim3((unsigned)blocks), dim3(threads), 0, stream, logits, ld, experts, top, chosen, weights, counts, rank, tokens);
+  return launch_ordered(route_kernel, dim3((unsigned)blocks), dim3(threads), 0, stream, logits, ld,
+                        experts, top, chosen, weights, counts, rank, tokens);
 }
 
 // out[t, o] = sum_i h[t, i] w[o, i] in fp32: h [tokens, width] of `dtype`, w fp32 [outputs,
@@ -383,7 +384,8 @@ SAKV_EXPORT int sakv_moe_plan(int32_t* counts, int32_t* offsets, int32_t* tile_e
                               int32_t* tile_row, int32_t* n_tiles, int experts, int max_tiles,
                               cudaStream_t stream) {
   if (experts <= 0 || experts > 1024 || max_tiles <= 0) return cudaErrorInvalidValue;
-  return launch_ordered(plan_kernel, dim3(1), dim3(256), (size_t)(experts + 1) * 4, stream, counts, offsets, tile_expert, tile_row, n_tiles, experts, max_tiles);
+  return launch_ordered(plan_kernel, dim3(1), dim3(256), (size_t)(experts + 1) * 4, stream, counts,
+                        offsets, tile_expert, tile_row, n_tiles, experts, max_tiles);
 }
 
 SAKV_EXPORT int sakv_moe_gather(const void* h, int dtype, const int32_t* chosen,
@@ -394,12 +396,12 @@ SAKV_EXPORT int sakv_moe_gather(const void* h, int dtype, const int32_t* chosen,
   if (tokens == 0) return 0;
   const dim3 grid((unsigned)((long long)tokens * top)), block(width >= 1024 ? 256 : 128);
   if (dtype == SAKV_F32)
-    return launch_ordered(gather_kernel<float>, grid, block, 0, stream, (const float*)h,
-                             chosen, weights, rank, offsets, (float*)rows, slot_of, top, width,
-                             weight_input);
+    return launch_ordered(gather_kernel<float>, grid, block, 0, stream, (const float*)h, chosen,
+                          weights, rank, offsets, (float*)rows, slot_of, top, width, weight_input);
   if (dtype == SAKV_BF16)
-    return launch_ordered(gather_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)h, chosen, weights, rank, offsets,
-                             (__nv_bfloat16*)rows, slot_of, top, width, weight_input);
+    return launch_ordered(gather_kernel<__nv_bfloat16>, grid, block, 0, stream,
+                          (const __nv_bfloat16*)h, chosen, weights, rank, offsets,
+                          (__nv_bfloat16*)rows, slot_of, top, width, weight_input);
   return cudaErrorInvalidValue;
 }
 
@@ -415,9 +417,9 @@ SAKV_EXPORT int sakv_moe_product(const void* a, int dtype, const void* w0, const
   const dim3 grid(max_tiles, (n + TN - 1) / TN), block(256);
   if (grid.y > 65535) return cudaErrorInvalidValue;
 #define SAKV_GROUPED(T, DUAL)                                                                    \
-  return launch_ordered(grouped_kernel<T, DUAL>, grid, block, 0, stream, (const T*)a,      \
-                           (const T*)w0, (const T*)w1, expert_stride, tile_expert, tile_row,     \
-                           offsets, n_tiles, out, n, k, limit, alpha)
+  return launch_ordered(grouped_kernel<T, DUAL>, grid, block, 0, stream, (const T*)a,          \
+                        (const T*)w0, (const T*)w1, expert_stride, tile_expert, tile_row,        \
+                        offsets, n_tiles, out, n, k, limit, alpha)
   if (dtype == SAKV_F32) {
     if (dual) SAKV_GROUPED(float, true);
     SAKV_GROUPED(float, false);
@@ -451,10 +453,12 @@ SAKV_EXPORT int sakv_clamped_act(const void* gate_up, void* out, int dtype, int 
   const long long count = (long long)tokens * ff;
   const dim3 grid(grid_for(count, 256)), block(256);
   if (dtype == SAKV_F32)
-    return launch_ordered(clamped_act_kernel<float>, grid, block, 0, stream, (const float*)gate_up, (float*)out, count, ff, limit, alpha);
+    return launch_ordered(clamped_act_kernel<float>, grid, block, 0, stream, (const float*)gate_up,
+                          (float*)out, count, ff, limit, alpha);
   if (dtype == SAKV_BF16)
-    return launch_ordered(clamped_act_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, count, ff, limit,
-                             alpha);
+    return launch_ordered(clamped_act_kernel<__nv_bfloat16>, grid, block, 0, stream,
+                          (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, count, ff, limit,
+                          alpha);
   return cudaErrorInvalidValue;
 }
 
@@ -467,7 +471,7 @@ SAKV_EXPORT int sakv_moe_combine(const float* rows, const int32_t* slot_of, cons
   if (tokens < 0 || top <= 0 || width <= 0) return cudaErrorInvalidValue;
   if (tokens == 0) return 0;
   const long long count = (long long)tokens * width;
-  return launch_ordered(combine_kernel, dim3(grid_for(count, 256)), dim3(256), 0, stream,
-                           rows, slot_of, weights, weight_output, shared, gate, gate_ld, out, top,
-                           width, count);
+  return launch_ordered(combine_kernel, dim3(grid_for(count, 256)), dim3(256), 0, stream, rows,
+                        slot_of, weights, weight_output, shared, gate, gate_ld, out, top, width,
+                        count);
 }

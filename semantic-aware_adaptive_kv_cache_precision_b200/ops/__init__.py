@@ -20,13 +20,13 @@ from . import mixture
 from .mixture import latent_prepare, rotate_heads
 from .attention import (attention_decode, attention_prefill, attention_prefill_tc, decode_splits,
                         forget_descriptors,
-                        fast_path_takes, kernel_errors, plan_key_splits, plan_token_blocks, plan_wide_tiles, tc_prefill_takes, upload_query_tiles,
+                        fast_path_takes, kernel_errors, plan_token_blocks, plan_wide_tiles, tc_prefill_takes, upload_query_tiles,
                         upload_wide_plan)
 
 __all__ = ["CACHE_BLOCK", "KernelError", "embed", "rms_norm", "rope_store", "attention_plain",
            "attention_decode", "attention_prefill", "attention_prefill_tc", "tc_prefill_takes", "plan_wide_tiles", "upload_wide_plan",
            "upload_query_tiles",
-           "decode_splits", "plan_key_splits", "plan_token_blocks", "fast_path_takes", "forget_descriptors",
+           "decode_splits", "plan_token_blocks", "fast_path_takes", "forget_descriptors",
            "kernel_errors", "gated_silu", "gelu_tanh", "streams_step", "streams_spread", "token_shift",
            "delta_rule", "kv_store", "layer_norm", "cached_attention", "mixture", "latent_prepare",
            "rotate_heads", "distance_attention", "gated_up", "gemm_tc", "add_into", "scale_cap_", "linear", "per_head", "choose", "Deferred"]

@@ -306,25 +306,6 @@ def kernel_errors() -> dict:
     return out
 
 
-def plan_key_splits(keys: int, items: int, wide: bool) -> tuple:
-    """(warps a block, blocks) that share the keys of one decoded token's heads in
-    `ops.cached_attention`: a warp for every chunk of 32 keys up to 16 a block (8 for values
-    wider than 256, which take more registers), then blocks until a warp walks at most two
-    chunks, as long as the grid stays within a few waves. (Measured at 8 tokens over 2,560
-    keys of 576 numbers: 4 blocks a token's head group 97 us, 16 blocks 156 us: the block
-    that comes last folds all the others' sums alone.) `keys`: the most keys a token can
-    see; `items`: tokens x groups of heads (a block each)."""
-    chunks = max(1, -(-int(keys) // 32))
-    cap = 8 if wide else 16
-    splits = 1
-    while splits < cap and splits < chunks:
-        splits *= 2
-    across = 1
-    while across < 16 and chunks > 2 * splits * across and 2 * items * across <= 8 * sm_count():
-        across *= 2
-    return splits, (across if splits > 1 else 1)
-
-
 def plan_token_blocks(keys: int, token_groups: int) -> int:
     """Blocks that share the chunks of one decoded token's keys in
     `ops.cached_attention(..., heads_first=True)`: one for every four chunks of 32 keys, up
